@@ -47,7 +47,7 @@ class KvGroup:
     v_pages: Dict[int, torch.Tensor] = field(default_factory=dict)
 
     def bytes_per_page(self, page_size: int, elem_size: int) -> int:
-        return 2 * len(self.members) * page_size * self.need.n_kv_heads * self.need.head_dim * elem_size
+        return len(self.members) * page_size * self.need.elements_per_token * elem_size
 
 
 @dataclass
@@ -110,9 +110,10 @@ class CacheManager:
     def _allocate_tensors(self) -> None:
         for g in self.groups:
             shape = (self.num_pages, g.need.n_kv_heads, self.page_size, g.need.head_dim)
+            v_shape = (self.num_pages, g.need.value_heads, self.page_size, g.need.value_dim)
             for n in g.members:
                 g.k_pages[n] = torch.zeros(shape, dtype=self.dtype, device=self.device)
-                g.v_pages[n] = torch.zeros(shape, dtype=self.dtype, device=self.device)
+                g.v_pages[n] = torch.zeros(v_shape, dtype=self.dtype, device=self.device)
         for n, need in self.state_needs.items():
             self.state_tensors[n] = torch.zeros((self.max_slots,) + tuple(need.shape), dtype=need.dtype, device=self.device)
 
@@ -122,7 +123,7 @@ class CacheManager:
         total = 0
         for need in needs:
             if isinstance(need, KvPagesNeed):
-                total += 2 * page_size * need.n_kv_heads * need.head_dim * elem_size
+                total += page_size * need.elements_per_token * elem_size
         return total
 
     def layer_cache(self, n: int) -> LayerCache:

@@ -87,6 +87,12 @@ def resolve_architecture(raw: dict) -> ArchEntry:
     if isinstance(names, str):
         names = [names]
     model_type = raw.get("model_type")
+    # a folder that names its design with a single ``architecture`` string (no task suffix: it generates text)
+    single = raw.get("architecture")
+    if isinstance(single, str):
+        entry = _find_by_alias(single)
+        if entry is not None:
+            return entry
     for name in names:
         if not isinstance(name, str) or "For" not in name:
             continue
@@ -107,7 +113,8 @@ def resolve_architecture(raw: dict) -> ArchEntry:
             return entry
     raise ConfigError(
         "unable to resolve model architecture from config metadata: "
-        f"architectures={list(names)!r}, model_type={model_type!r}; known: {registered_architectures()}")
+        f"architectures={list(names)!r}, architecture={single!r}, model_type={model_type!r}; "
+        f"known: {registered_architectures()}")
 
 
 def extract_eos_token_ids(raw: dict, required: bool = False) -> Tuple[int, ...]:

@@ -19,10 +19,14 @@ from typing import Optional, Tuple
 
 @dataclass(frozen=True)
 class NormSpec:
-    """Root-mean-square norm over ``dim`` with a learned scale."""
+    """Root-mean-square norm over ``dim`` with a learned scale: x / sqrt(mean(x^2) + eps) * (offset + w).
+    ``offset`` is 0 where the scale is stored as it is applied and 1 where it is stored around zero;
+    ``suffix`` is what follows the part's prefix in the tensor's name."""
     dim: int
     eps: float
     kind: str = "rmsnorm"
+    offset: float = 0.0
+    suffix: str = ".weight"
 
 
 @dataclass(frozen=True)
@@ -57,6 +61,78 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class QueryTemperatureSpec:
+    """Queries at position p are scaled by 1 + coef * ln(floor((p + 1) / every) + 1): attention sharpens
+    as a sequence grows, in steps of ``every`` positions."""
+    coef: float
+    every: int
+
+
+@dataclass(frozen=True)
+class DiffAttentionSpec:
+    """Differential attention over a paged cache: every query head holds two score maps (two queries and two
+    keys of ``head_dim``) over the same values of ``value_dim``; the head's output is map 1 minus lambda
+    times map 2, divided by its root mean square and scaled by ``1 - lambda_init``, with
+    lambda = exp(<lq1, lk1>) - exp(<lq2, lk2>) + lambda_init.  ``gated``: the concatenated heads are
+    multiplied with sigmoid of a projection of the mixer's input before the output projection.
+    The ``*_name`` fields are the tensors' names below the mixer's prefix."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    softmax_scale: float
+    lambda_init: float
+    norm_eps: float
+    query_temperature: Optional[QueryTemperatureSpec] = None
+    gated: bool = True
+    window: Optional[int] = None
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    gate_name: str = "g"
+    o_name: str = "o"
+    lambda_names: Tuple[str, str, str, str] = ("lq1", "lk1", "lq2", "lk2")
+    kind: str = "diff_attention"
+
+
+@dataclass(frozen=True)
+class ClampedGluSpec:
+    """down(a * sigmoid(alpha * a) * (b + 1)) with a = min(gate(x), limit), b = clamp(up(x), -limit, limit); no biases."""
+    hidden_size: int
+    intermediate_size: int
+    limit: float
+    alpha: float = 1.702
+    gate_name: str = "gate"
+    up_name: str = "up"
+    down_name: str = "down"
+    kind: str = "clamped_glu"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of ``n_experts`` SiLU-gated feed-forwards of ``expert_size``, ``top_k`` per token.  The router's
+    scores are sigmoid(W_router x) in 32-bit.  Experts form ``n_groups`` equal runs of neighbours; a group's
+    score is the sum of its ``group_score_top`` largest scores, and only experts of the ``keep_groups`` best
+    groups can be chosen.  The chosen experts' outputs are added up weighted by their scores
+    (``renormalize``: divided by the scores' sum first).  Expert e's tensors are ``<prefix>.<expert_prefix><e>.<name>``."""
+    hidden_size: int
+    expert_size: int
+    n_experts: int
+    top_k: int
+    n_groups: int = 1
+    keep_groups: int = 1
+    group_score_top: int = 2
+    renormalize: bool = False
+    router_name: str = "router"
+    expert_prefix: str = "e"
+    gate_name: str = "gate"
+    up_name: str = "up"
+    down_name: str = "down"
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
 class GatedMlpSpec:
     """down(act(gate(x)) * up(x)), no biases."""
     hidden_size: int
@@ -82,6 +158,12 @@ class BlockSpec:
     mixer_norm_name: str = "input_layernorm"
     ff_norm_name: str = "post_attention_layernorm"
     kind: str = "prenorm_residual"
+    # kind "sandwich_residual": a norm after each sublayer as well, applied to its output before the residual add;
+    # there ``feed_forward`` (with its norms) may be None: a layer that is a mixer only
+    mixer_post_norm: Optional[NormSpec] = None
+    ff_post_norm: Optional[NormSpec] = None
+    mixer_post_norm_name: str = "post_mixer_norm"
+    ff_post_norm_name: str = "post_ff_norm"
 
 
 @dataclass(frozen=True)
@@ -91,6 +173,17 @@ class TokenEmbeddingSpec:
     hidden_size: int
     name: str = "model.embed_tokens.weight"
     kind: str = "token_embedding"
+
+
+@dataclass(frozen=True)
+class SinusoidEmbeddingSpec:
+    """The token's row of the table plus a fixed position vector: entry 2i is sin(p * base^(-2i/hidden_size)),
+    entry 2i + 1 the cosine of the same angle, p the token's position in its sequence."""
+    vocab_size: int
+    hidden_size: int
+    name: str = "model.embed_tokens.weight"
+    base: float = 10000.0
+    kind: str = "token_embedding_sinusoid"
 
 
 @dataclass(frozen=True)

@@ -61,3 +61,34 @@ PB_API int pb_silu_mul(const void* gate_up, void* out, int dtype, int n_tokens, 
     PB_CHECK_LAUNCH("silu_mul");
     return 0;
 }
+
+// Clamped gated unit on a merged gate/up projection:
+//   a = min(gu[t, i], limit), b = clamp(gu[t, I + i], -limit, limit), out[t, i] = a * sigmoid(alpha * a) * (b + 1)
+// in float32, rounded once.
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long n_tokens, int inter,
+                                   float limit, float alpha) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_tokens * inter) return;
+    long long t = idx / inter;
+    int i = (int)(idx % inter);
+    float a = fminf(pb_ld(gu + t * 2 * inter + i), limit);
+    float b = fminf(fmaxf(pb_ld(gu + t * 2 * inter + inter + i), -limit), limit);
+    pb_st(out + idx, a / (1.0f + expf(-alpha * a)) * (b + 1.0f));
+}
+
+PB_API int pb_clamped_glu(const void* gate_up, void* out, int dtype, int n_tokens, int inter, float limit, float alpha,
+                          cudaStream_t stream) {
+    PB_REQUIRE(n_tokens >= 0 && inter > 0 && limit > 0.f, "clamped_glu: bad sizes T=%d I=%d limit=%g", n_tokens, inter, limit);
+    if (n_tokens == 0) return 0;
+    const int threads = 256;
+    long long n = (long long)n_tokens * inter;
+    PB_REQUIRE((n + threads - 1) / threads < (1ll << 31), "clamped_glu: too many elements");
+    PB_DISPATCH_DTYPE(dtype, T,
+        (pb_launch(clamped_glu_kernel<T>, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, stream,
+            (const T*)gate_up, (T*)out, (long long)n_tokens, inter, limit, alpha)));
+    PB_CHECK_LAUNCH("clamped_glu");
+    return 0;
+}

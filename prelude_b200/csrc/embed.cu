@@ -58,3 +58,42 @@ PB_API int pb_embed_gather(const int32_t* ids, const void* table, int table_dtyp
     PB_CHECK_LAUNCH("embed_gather");
     return 0;
 }
+
+// Embedding plus a fixed sinusoidal position vector:
+//   res[t, 2i] = table[ids[t], 2i] + sin(p_t * rate[i]),  res[t, 2i + 1] = table[ids[t], 2i + 1] + cos(p_t * rate[i])
+// with rate[i] = base^(-2i / width), made by the host in 64-bit.  The angle is a product of an integer below 2^24
+// and a rate; it and its sine and cosine are taken in 64-bit, so that a position in the thousands loses nothing
+// to the rounding of the angle, and the sum is rounded once to the float32 residual stream.
+template <typename T>
+__global__ void embed_sinusoid_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ positions,
+                                      const T* __restrict__ table, const double* __restrict__ rate,
+                                      float* __restrict__ out, int n_tokens, int width, int vocab) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    int t = blockIdx.x;
+    if (t >= n_tokens) return;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const double p = (double)positions[t];
+    const T* src = table + (size_t)(ok ? id : 0) * width;
+    float* dst = out + (size_t)t * width;
+    for (int i = threadIdx.x; i < (width + 1) / 2; i += blockDim.x) {
+        double s, c;
+        sincos(p * rate[i], &s, &c);
+        dst[2 * i] = (float)((ok ? (double)pb_ld(src + 2 * i) : 0.0) + s);
+        if (2 * i + 1 < width) dst[2 * i + 1] = (float)((ok ? (double)pb_ld(src + 2 * i + 1) : 0.0) + c);
+    }
+}
+
+PB_API int pb_embed_sinusoid(const int32_t* ids, const int32_t* positions, const void* table, int table_dtype,
+                             const double* rate, float* out, int n_tokens, int width, int vocab, cudaStream_t stream) {
+    PB_REQUIRE(n_tokens >= 0 && width > 0 && vocab > 0, "embed_sinusoid: bad sizes T=%d H=%d V=%d", n_tokens, width, vocab);
+    PB_REQUIRE(ids && positions && table && rate && out, "embed_sinusoid: null pointer");
+    if (n_tokens == 0) return 0;
+    int threads = width >= 1024 ? 256 : 128;
+    PB_DISPATCH_DTYPE(table_dtype, T,
+        (pb_launch(embed_sinusoid_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, ids, positions, (const T*)table, rate, out,
+                   n_tokens, width, vocab)));
+    PB_CHECK_LAUNCH("embed_sinusoid");
+    return 0;
+}

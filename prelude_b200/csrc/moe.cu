@@ -1,0 +1,409 @@
+// Routed experts: the router's choice, the grouping of a step's (token, choice) pairs by expert, the experts'
+// products over those groups, and the weighted sum of a token's choices.  Nothing here decides on the host:
+// counts, offsets and the map from tiles to experts stay on the device, so a step through a mixture of experts
+// has the shape of its token count alone and can be recorded.
+//
+//   route    scores s = sigmoid(z) of float32 router logits; experts form `groups` equal runs of neighbours, a
+//            group's score is the sum of its `gtop` largest scores, only experts of the `keep` best groups can
+//            be chosen; the `top` largest allowed scores are chosen (ties: the smaller index), their weights are
+//            the scores themselves (or, with `renorm`, divided by their sum).
+//   sort     slot i = token * top + choice.  The slots are grouped by expert: offsets[e] .. offsets[e + 1] are the
+//            places of expert e, order[place] = slot, place_of[slot] = place, and the places are cut into row
+//            tiles of MOE_BM that never span two experts (tile_expert, tile_row0; -1 behind the last tile).
+//   products h[place] = silu(Wg_e x) * (Wu_e x) with x the row of slot / top, then y[place] = Wd_e h[place].
+//            An output element is summed over k in ascending order by one thread (float32 units) or one
+//            tensor-core accumulator (bfloat16), whatever its place in the tile, so a token's result does not
+//            depend on who else chose the expert.
+//   combine  out[t] = sum over choices c, in order, of w[t, c] * y[place_of[t * top + c]], in float32.
+#include "common.cuh"
+
+#include <math.h>
+#include <mma.h>
+
+#define MOE_BM 64
+#define MOE_BN 64
+#define MOE_BK 16
+#define MOE_MAX_TOP 32
+#define MOE_MAX_GROUPS 64
+#define MOE_MAX_GTOP 8
+#define MOE_MAX_EXPERTS 1024
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int groups, int keep,
+                                 int gtop, int renorm, int32_t* __restrict__ ids, float* __restrict__ weights) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_tokens) return;
+    const float* z = logits + (size_t)t * n_experts;
+    const int per = n_experts / groups;
+    unsigned long long allowed = groups >= 64 ? ~0ull : ((1ull << groups) - 1ull);
+    if (keep < groups) {
+        float gscore[MOE_MAX_GROUPS];
+        for (int g = 0; g < groups; ++g) {
+            // the sum of the group's gtop largest scores
+            int taken[MOE_MAX_GTOP];
+            float sum = 0.f;
+            const int n = min(gtop, per);
+            for (int r = 0; r < n; ++r) {
+                int best = -1;
+                float bs = 0.f;
+                for (int i = 0; i < per; ++i) {
+                    bool used = false;
+                    for (int u = 0; u < r; ++u) used |= taken[u] == i;
+                    if (used) continue;
+                    const float s = 1.0f / (1.0f + expf(-z[g * per + i]));
+                    if (best < 0 || s > bs) { best = i; bs = s; }
+                }
+                taken[r] = best;
+                sum += bs;
+            }
+            gscore[g] = sum;
+        }
+        allowed = 0ull;
+        for (int r = 0; r < keep; ++r) {
+            int best = -1;
+            for (int g = 0; g < groups; ++g) {
+                if ((allowed >> g) & 1ull) continue;
+                if (best < 0 || gscore[g] > gscore[best]) best = g;
+            }
+            allowed |= 1ull << best;
+        }
+    }
+    int chosen[MOE_MAX_TOP];
+    float score[MOE_MAX_TOP];
+    float total = 0.f;
+    for (int r = 0; r < top; ++r) {
+        int best = -1;
+        float bs = 0.f;
+        for (int e = 0; e < n_experts; ++e) {
+            if (!((allowed >> (e / per)) & 1ull)) continue;
+            bool used = false;
+            for (int u = 0; u < r; ++u) used |= chosen[u] == e;
+            if (used) continue;
+            const float s = 1.0f / (1.0f + expf(-z[e]));
+            if (best < 0 || s > bs) { best = e; bs = s; }
+        }
+        chosen[r] = best;
+        score[r] = bs;
+        total += bs;
+    }
+    for (int r = 0; r < top; ++r) {
+        ids[(size_t)t * top + r] = chosen[r];
+        weights[(size_t)t * top + r] = renorm ? score[r] / total : score[r];
+    }
+}
+
+PB_API int pb_moe_route(const float* logits, int n_tokens, int n_experts, int top, int groups, int keep, int gtop, int renorm,
+                        int32_t* ids, float* weights, cudaStream_t stream) {
+    PB_REQUIRE(n_tokens >= 0 && n_experts > 0 && n_experts <= MOE_MAX_EXPERTS && top > 0 && top <= MOE_MAX_TOP,
+               "moe_route: bad sizes T=%d E=%d top=%d", n_tokens, n_experts, top);
+    PB_REQUIRE(groups > 0 && groups <= MOE_MAX_GROUPS && n_experts % groups == 0 && keep > 0 && keep <= groups && gtop > 0 &&
+               gtop <= MOE_MAX_GTOP, "moe_route: %d groups, keep %d, group score over %d", groups, keep, gtop);
+    PB_REQUIRE(top <= keep * (n_experts / groups), "moe_route: top=%d experts cannot come from %d groups of %d", top, keep, n_experts / groups);
+    PB_REQUIRE(logits && ids && weights, "moe_route: null pointer");
+    if (n_tokens == 0) return 0;
+    pb_launch(moe_route_kernel, dim3((n_tokens + 63) / 64), dim3(64), 0, stream, logits, n_tokens, n_experts, top, groups, keep, gtop,
+              renorm, ids, weights);
+    PB_CHECK_LAUNCH("moe_route");
+    return 0;
+}
+
+// One block.  ids [n_slots] in [0, n_experts); offsets [n_experts + 1]; order, place_of [n_slots];
+// tile_expert, tile_row0 [max_tiles], max_tiles >= ceil(n_slots / MOE_BM) + n_experts.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t* __restrict__ ids, int n_slots, int n_experts,
+                                                        int32_t* __restrict__ offsets, int32_t* __restrict__ order,
+                                                        int32_t* __restrict__ place_of, int32_t* __restrict__ tile_expert,
+                                                        int32_t* __restrict__ tile_row0, int max_tiles) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS + 1], tile0[MOE_MAX_EXPERTS + 1];
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
+        const int e = min(max(ids[i], 0), n_experts - 1);
+        atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            start[e] = at;
+            tile0[e] = tiles;
+            at += count[e];
+            tiles += (count[e] + MOE_BM - 1) / MOE_BM;
+        }
+        start[n_experts] = at;
+        tile0[n_experts] = tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) offsets[e] = start[e];
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        for (int k = 0, n = tile0[e + 1] - tile0[e]; k < n; ++k) {
+            if (tile0[e] + k < max_tiles) {
+                tile_expert[tile0[e] + k] = e;
+                tile_row0[tile0[e] + k] = start[e] + k * MOE_BM;
+            }
+        }
+        count[e] = 0;                                       // now the cursor of the expert's places
+    }
+    for (int i = tile0[n_experts] + threadIdx.x; i < max_tiles; i += blockDim.x) {
+        tile_expert[i] = -1;
+        tile_row0[i] = 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
+        const int e = min(max(ids[i], 0), n_experts - 1);
+        const int place = start[e] + atomicAdd(&count[e], 1);
+        order[place] = i;
+        place_of[i] = place;
+    }
+}
+
+PB_API int pb_moe_tile_rows() { return MOE_BM; }
+
+PB_API int pb_moe_sort(const int32_t* ids, int n_slots, int n_experts, int32_t* offsets, int32_t* order, int32_t* place_of,
+                       int32_t* tile_expert, int32_t* tile_row0, int max_tiles, cudaStream_t stream) {
+    PB_REQUIRE(n_slots >= 0 && n_experts > 0 && n_experts <= MOE_MAX_EXPERTS, "moe_sort: bad sizes slots=%d E=%d", n_slots, n_experts);
+    PB_REQUIRE(max_tiles >= (n_slots + MOE_BM - 1) / MOE_BM + n_experts, "moe_sort: room for %d tiles is too little", max_tiles);
+    PB_REQUIRE(ids && offsets && order && place_of && tile_expert && tile_row0, "moe_sort: null pointer");
+    pb_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, ids, n_slots, n_experts, offsets, order, place_of, tile_expert,
+              tile_row0, max_tiles);
+    PB_CHECK_LAUNCH("moe_sort");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The experts' products on the float32 units (the 32-bit path; also bfloat16 storage with float32 arithmetic).
+// C[place, n] = sum_k A[src(place), k] * W_e[n, k]; gated: silu(sum with gate rows) * (sum with up rows), the
+// expert's weight being [2 N, K], gate rows first.  src(place) = order[place] / a_div when `order` is given (the
+// token of a slot), else the place itself.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T, typename TC, bool GATED>
+__global__ void __launch_bounds__(256) moe_gemm_fma_kernel(const T* __restrict__ A, long long lda, const int32_t* __restrict__ order,
+                                                           int a_div, const T* __restrict__ W, long long w_expert_stride, int N,
+                                                           int K, const int32_t* __restrict__ tile_expert,
+                                                           const int32_t* __restrict__ tile_row0,
+                                                           const int32_t* __restrict__ offsets, TC* __restrict__ C, long long ldc) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int row0 = tile_row0[blockIdx.x], row_end = offsets[e + 1];
+    const int n0 = blockIdx.y * MOE_BN;
+    __shared__ float As[MOE_BK][MOE_BM + 1];
+    __shared__ float Ws[GATED ? 2 : 1][MOE_BK][MOE_BN + 1];
+    __shared__ int src_s[MOE_BM];
+    const int tid = threadIdx.x;
+    if (tid < MOE_BM) {
+        const int p = row0 + tid;
+        src_s[tid] = p < row_end ? (order ? order[p] / a_div : p) : -1;
+    }
+    __syncthreads();
+    const int tx = tid % 16, ty = tid / 16;
+    const T* We = W + (size_t)e * w_expert_stride;
+    float acc[GATED ? 2 : 1][4][4];
+#pragma unroll
+    for (int g = 0; g < (GATED ? 2 : 1); ++g)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[g][i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int idx = tid + r * 256;
+            const int row = idx / MOE_BK, kk = idx % MOE_BK;
+            const int gk = k0 + kk, gn = n0 + row;
+            const int src = src_s[row];
+            As[kk][row] = (src >= 0 && gk < K) ? pb_ld(A + (size_t)src * lda + gk) : 0.f;
+            Ws[0][kk][row] = (gn < N && gk < K) ? pb_ld(We + (size_t)gn * K + gk) : 0.f;
+            if (GATED) Ws[GATED ? 1 : 0][kk][row] = (gn < N && gk < K) ? pb_ld(We + (size_t)(N + gn) * K + gk) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; ++kk) {
+            float a[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int g = 0; g < (GATED ? 2 : 1); ++g) {
+                float b[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = Ws[g][kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[g][i][j] = fmaf(a[i], b[j], acc[g][i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int p = row0 + ty * 4 + i;
+        if (p >= row_end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= N) continue;
+            float v = acc[0][i][j];
+            if (GATED) v = v / (1.0f + expf(-v)) * acc[GATED ? 1 : 0][i][j];
+            pb_st(C + (size_t)p * ldc + gn, v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same products on the tensor cores: bfloat16 operands, float32 accumulators (mma.sync m16n8k16 through the
+// warp-matrix interface), 64 x 64 tiles, eight warps each owning a 16 x 32 piece (gated: of both products).
+// Rows of A are gathered through `order`; K in steps of 32 with 16-byte loads.  Needs K % 8 == 0.
+// ---------------------------------------------------------------------------------------------------------------
+#define MOE_TK 32
+#define MOE_LD (MOE_TK + 8)
+
+template <typename TC, bool GATED>
+__global__ void __launch_bounds__(256) moe_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, long long lda,
+                                                            const int32_t* __restrict__ order, int a_div,
+                                                            const __nv_bfloat16* __restrict__ W, long long w_expert_stride, int N,
+                                                            int K, const int32_t* __restrict__ tile_expert,
+                                                            const int32_t* __restrict__ tile_row0,
+                                                            const int32_t* __restrict__ offsets, TC* __restrict__ C, long long ldc) {
+    using namespace nvcuda;
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int row0 = tile_row0[blockIdx.x], row_end = offsets[e + 1];
+    const int n0 = blockIdx.y * MOE_BN;
+    __shared__ __align__(32) __nv_bfloat16 As[MOE_BM][MOE_LD];
+    __shared__ __align__(32) __nv_bfloat16 Ws[GATED ? 2 : 1][MOE_BN][MOE_LD];
+    __shared__ __align__(32) float Cs[8][16][36];
+    __shared__ int src_s[MOE_BM];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < MOE_BM) {
+        const int p = row0 + tid;
+        src_s[tid] = p < row_end ? (order ? order[p] / a_div : p) : -1;
+    }
+    __syncthreads();
+    const __nv_bfloat16* We = W + (size_t)e * w_expert_stride;
+    const int wm = warp / 2, wn = warp % 2;                  // the warp's piece: rows 16 wm .., columns 32 wn ..
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[GATED ? 2 : 1][2];
+#pragma unroll
+    for (int g = 0; g < (GATED ? 2 : 1); ++g)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) wmma::fill_fragment(acc[g][j], 0.f);
+    const int lr = tid / 4, lc = (tid % 4) * 8;               // this thread's 16-byte piece of a 64 x 32 tile
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int k0 = 0; k0 < K; k0 += MOE_TK) {
+        const bool kin = k0 + lc < K;
+        const int src = src_s[lr];
+        *reinterpret_cast<uint4*>(&As[lr][lc]) = (src >= 0 && kin) ? *reinterpret_cast<const uint4*>(A + (size_t)src * lda + k0 + lc) : zero;
+        const int gn = n0 + lr;
+        *reinterpret_cast<uint4*>(&Ws[0][lr][lc]) = (gn < N && kin) ? *reinterpret_cast<const uint4*>(We + (size_t)gn * K + k0 + lc) : zero;
+        if (GATED)
+            *reinterpret_cast<uint4*>(&Ws[GATED ? 1 : 0][lr][lc]) =
+                (gn < N && kin) ? *reinterpret_cast<const uint4*>(We + (size_t)(N + gn) * K + k0 + lc) : zero;
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_TK; kk += 16) {
+            wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
+            wmma::load_matrix_sync(a, &As[wm * 16][kk], MOE_LD);
+#pragma unroll
+            for (int g = 0; g < (GATED ? 2 : 1); ++g)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> b;
+                    wmma::load_matrix_sync(b, &Ws[g][wn * 32 + j * 16][kk], MOE_LD);
+                    wmma::mma_sync(acc[g][j], a, b, acc[g][j]);
+                }
+        }
+        __syncthreads();
+    }
+    if (GATED) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int i = 0; i < acc[0][j].num_elements; ++i) {
+                const float v = acc[0][j].x[i];
+                acc[0][j].x[i] = v / (1.0f + expf(-v)) * acc[GATED ? 1 : 0][j].x[i];
+            }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) wmma::store_matrix_sync(&Cs[warp][0][j * 16], acc[0][j], 36, wmma::mem_row_major);
+    __syncwarp();
+    for (int i = lane; i < 16 * 32; i += 32) {
+        const int r = i / 32, c = i % 32;
+        const int p = row0 + wm * 16 + r, gn = n0 + wn * 32 + c;
+        if (p < row_end && gn < N) pb_st(C + (size_t)p * ldc + gn, Cs[warp][r][c]);
+    }
+}
+
+// A [*, K] with row stride lda; order null or int32 [places]; W [E, (2) N, K] dense, w_expert_stride elements from one
+// expert to the next; C [places, N] with row stride ldc, of type out_dtype (float32 or the input's).  grid: max_tiles.
+PB_API int pb_moe_gemm(const void* A, long long lda, const int32_t* order, int a_div, const void* W, long long w_expert_stride,
+                       int N, int K, int gated, const int32_t* tile_expert, const int32_t* tile_row0, const int32_t* offsets,
+                       int max_tiles, void* C, long long ldc, int dtype, int out_dtype, cudaStream_t stream) {
+    PB_REQUIRE(N > 0 && K > 0 && max_tiles >= 0 && a_div > 0, "moe_gemm: bad sizes N=%d K=%d", N, K);
+    PB_REQUIRE(lda >= K && ldc >= N && w_expert_stride >= (long long)(gated ? 2 : 1) * N * K, "moe_gemm: a stride is shorter than its row");
+    PB_REQUIRE(A && W && C && tile_expert && tile_row0 && offsets, "moe_gemm: null pointer");
+    PB_REQUIRE(out_dtype == PB_F32 || out_dtype == dtype, "moe_gemm: output is float32 or of the input's type");
+    if (max_tiles == 0) return 0;
+    dim3 grid(max_tiles, (N + MOE_BN - 1) / MOE_BN);
+    PB_REQUIRE(grid.y < 65536, "moe_gemm: N=%d too large", N);
+#define MOE_LAUNCH(KERNEL, TA, TCC, G)                                                                                         \
+    pb_launch(KERNEL, grid, dim3(256), 0, stream, (const TA*)A, lda, order, a_div, (const TA*)W, w_expert_stride, N, K, tile_expert, \
+              tile_row0, offsets, (TCC*)C, ldc)
+    if (dtype == PB_F32) {
+        if (gated) MOE_LAUNCH((moe_gemm_fma_kernel<float, float, true>), float, float, 1);
+        else MOE_LAUNCH((moe_gemm_fma_kernel<float, float, false>), float, float, 0);
+    } else if (dtype == PB_BF16) {
+        const bool tc = K % 8 == 0 && lda % 8 == 0 && w_expert_stride % 8 == 0 && pb_aligned(A, 16) && pb_aligned(W, 16);
+        if (tc) {
+            if (out_dtype == PB_F32) {
+                if (gated) MOE_LAUNCH((moe_gemm_bf16_kernel<float, true>), __nv_bfloat16, float, 1);
+                else MOE_LAUNCH((moe_gemm_bf16_kernel<float, false>), __nv_bfloat16, float, 0);
+            } else {
+                if (gated) MOE_LAUNCH((moe_gemm_bf16_kernel<__nv_bfloat16, true>), __nv_bfloat16, __nv_bfloat16, 1);
+                else MOE_LAUNCH((moe_gemm_bf16_kernel<__nv_bfloat16, false>), __nv_bfloat16, __nv_bfloat16, 0);
+            }
+        } else {
+            if (out_dtype == PB_F32) {
+                if (gated) MOE_LAUNCH((moe_gemm_fma_kernel<__nv_bfloat16, float, true>), __nv_bfloat16, float, 1);
+                else MOE_LAUNCH((moe_gemm_fma_kernel<__nv_bfloat16, float, false>), __nv_bfloat16, float, 0);
+            } else {
+                if (gated) MOE_LAUNCH((moe_gemm_fma_kernel<__nv_bfloat16, __nv_bfloat16, true>), __nv_bfloat16, __nv_bfloat16, 1);
+                else MOE_LAUNCH((moe_gemm_fma_kernel<__nv_bfloat16, __nv_bfloat16, false>), __nv_bfloat16, __nv_bfloat16, 0);
+            }
+        }
+    } else {
+        return pb_fail("moe_gemm: unknown element type code %d", dtype);
+    }
+#undef MOE_LAUNCH
+    PB_CHECK_LAUNCH("moe_gemm");
+    return 0;
+}
+
+// out[t, :] = sum_c w[t, c] * y[place_of[t * top + c], :], choices in ascending order, float32 sums.
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ place_of,
+                                   const float* __restrict__ weights, T* __restrict__ out, int top, int width) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const size_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = 0.f;
+        for (int c = 0; c < top; ++c) v = fmaf(weights[t * top + c], y[(size_t)place_of[t * top + c] * width + i], v);
+        pb_st(out + t * width + i, v);
+    }
+}
+
+PB_API int pb_moe_combine(const float* y, const int32_t* place_of, const float* weights, void* out, int dtype, int n_tokens,
+                          int top, int width, cudaStream_t stream) {
+    PB_REQUIRE(n_tokens >= 0 && top > 0 && width > 0, "moe_combine: bad sizes");
+    PB_REQUIRE(y && place_of && weights && out, "moe_combine: null pointer");
+    if (n_tokens == 0) return 0;
+    PB_DISPATCH_DTYPE(dtype, T,
+        (pb_launch(moe_combine_kernel<T>, dim3(n_tokens), dim3(width >= 1024 ? 256 : 128), 0, stream, y, place_of, weights, (T*)out, top, width)));
+    PB_CHECK_LAUNCH("moe_combine");
+    return 0;
+}

@@ -319,3 +319,64 @@ PB_API int pb_rmsnorm(const void* x, const float* w, void* y, int dtype, int row
     PB_CHECK_LAUNCH("rmsnorm");
     return 0;
 }
+
+// A sublayer's output that is normed before it joins the residual stream, fused with the norm that follows:
+//   res += x / sqrt(mean(x^2) + eps_x) * wx ;  y = res / sqrt(mean(res^2) + eps) * w
+// one block per row, all in float32; x is rounded nowhere between its norm and the sum.  Without w and y only the
+// sum is made.  With `rows` (the gather form) row i of y is made from row rows[i] of x and res, and res is left alone.
+// The row is kept in shared memory between the passes where it fits, else it is read again.
+template <typename TX, typename TY>
+__global__ void normed_add_rmsnorm_kernel(const TX* __restrict__ x, const float* __restrict__ wx, float eps_x,
+                                          float* __restrict__ res, const int32_t* __restrict__ rows, int n_rows_total,
+                                          const float* __restrict__ w, TY* __restrict__ y, int width, float eps, int keep) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    extern __shared__ float row_s[];
+    __shared__ float red[32];
+    const long long src = rows ? (long long)rows[blockIdx.x] : (long long)blockIdx.x;
+    TY* out = y ? y + (size_t)blockIdx.x * width : nullptr;
+    if (src < 0 || src >= n_rows_total) {
+        if (out) for (int i = threadIdx.x; i < width; i += blockDim.x) pb_st(out + i, 0.f);
+        return;
+    }
+    const TX* xr = x + (size_t)src * width;
+    float* r = res + (size_t)src * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = pb_ld(xr + i);
+        if (keep) row_s[i] = v;
+        ss += v * v;
+    }
+    const float inv_x = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps_x);
+    ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = r[i] + (keep ? row_s[i] : pb_ld(xr + i)) * inv_x * wx[i];
+        if (rows == nullptr) r[i] = v;
+        if (keep) row_s[i] = v;
+        ss += v * v;
+    }
+    if (out == nullptr) return;
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = keep ? row_s[i] : (rows == nullptr ? r[i] : r[i] + pb_ld(xr + i) * inv_x * wx[i]);
+        pb_st(out + i, v * inv * w[i]);
+    }
+}
+
+// x [n_rows_total, width] of type dtype; wx, w float32 [width]; res float32 [n_rows_total, width]; rows null (every
+// row, res updated) or int32 [n_out] (those rows, res untouched); y [n_out, width] of type dtype, or null with w.
+PB_API int pb_normed_add_rmsnorm(const void* x, const float* wx, float eps_x, float* res, const int32_t* rows, int n_out,
+                                 int n_rows_total, const float* w, void* y, int dtype, int width, float eps,
+                                 cudaStream_t stream) {
+    PB_REQUIRE(n_out >= 0 && n_rows_total >= 0 && width > 0, "normed_add_rmsnorm: bad sizes");
+    PB_REQUIRE(x && wx && res && ((w == nullptr) == (y == nullptr)), "normed_add_rmsnorm: null pointer");
+    PB_REQUIRE(rows == nullptr ? n_out == n_rows_total : y != nullptr, "normed_add_rmsnorm: rows and outputs do not fit");
+    if (n_out == 0) return 0;
+    const int keep = (size_t)width * sizeof(float) <= 40 * 1024 ? 1 : 0;
+    const size_t smem = keep ? (size_t)width * sizeof(float) : 0;
+    PB_DISPATCH_DTYPE(dtype, T,
+        (pb_launch(normed_add_rmsnorm_kernel<T, T>, dim3(n_out), dim3(norm_threads(width)), smem, stream, (const T*)x, wx, eps_x,
+                   res, rows, n_rows_total, w, (T*)y, width, eps, keep)));
+    PB_CHECK_LAUNCH("normed_add_rmsnorm");
+    return 0;
+}

@@ -27,14 +27,14 @@ from .runner import StepEntry
 
 
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, page_size: int = 16,
-           device: str = "cuda:0", say=print) -> int:
+           device: str = "cuda:0", say=print, max_requests: int = 4) -> int:
     """Run the steps that ``lines`` yields; returns the number of steps run."""
     import numpy as np
 
     os.makedirs(out_dir, exist_ok=True)
     model = load_model(model_dir, dtype, device)
     # every live request's count is rounded up to a multiple of 64 by the caller; pages divide 64
-    runner = make_runner(model, page_size=page_size, num_pages=max(1, -(-max_tokens // page_size)), max_slots=64,
+    runner = make_runner(model, page_size=page_size, num_pages=max(1, -(-max_tokens // page_size)), max_slots=max_requests,
                          max_request_tokens=max_tokens)
     runner.enable_step_graphs()               # as generation runs them: steps with prompt tokens replay captured pieces
     n = 0
@@ -74,6 +74,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (must divide 64)")
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: the most requests live at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     if args.page_size <= 0 or 64 % args.page_size:
@@ -86,7 +87,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         sys.stdout.flush()
 
     try:
-        replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, args.page_size, args.device, say)
+        replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, args.page_size, args.device, say,
+               max_requests=max(1, args.max_requests))
     except Exception as e:  # noqa: BLE001 - one line for the user, non-zero exit
         sys.stderr.write(f"trace_run: {type(e).__name__}: {e}\n")
         return 1

@@ -62,6 +62,64 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Ten
     return out
 
 
+def embed_sinusoid(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, rate: torch.Tensor,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """res[t, 2i] = table[ids[t], 2i] + sin(p_t rate[i]), res[t, 2i+1] = table[ids[t], 2i+1] + cos(p_t rate[i]), float32;
+    ``rate`` is float64 [ceil(width / 2)]."""
+    _need(ids, "ids", torch.int32)
+    _need(positions, "positions", torch.int32)
+    _need(table, "table")
+    _need(rate, "rate", torch.float64)
+    T, (V, H) = ids.numel(), table.shape
+    if positions.numel() != T or rate.numel() != (H + 1) // 2:
+        raise KernelLibraryError("embed_sinusoid: one position per token and one rate per pair of columns")
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    check(_l.library().pb_embed_sinusoid(ids.data_ptr(), positions.data_ptr(), table.data_ptr(), dtype_code(table.dtype),
+                                         rate.data_ptr(), out.data_ptr(), T, H, V, _stream()), "embed_sinusoid")
+    return out
+
+
+class Normed:
+    """A sublayer's output that is normed before it joins the residual stream: the value is
+    ``x / sqrt(mean(x^2) + eps) * weight`` (weight float32, as applied), not computed yet.  The fused residual
+    add takes it as it is and norms, adds and norms again in one pass, in float32."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float):
+        self.x, self.weight, self.eps = x, weight, float(eps)
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+
+def normed_add_rmsnorm(x: "Normed", res: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                       rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """res += norm(x) (in place, unless ``rows`` picks rows: then res is left alone); returns rmsnorm(res) * weight
+    in ``out_dtype`` for every row, or for the chosen ones; with ``weight`` None only the sum is made."""
+    xt = x.x.materialize(out_dtype) if isinstance(x.x, PartialSums) else x.x
+    _need(xt, "x", out_dtype)
+    _need(x.weight, "x.weight", torch.float32)
+    _need(res, "res", torch.float32)
+    total, width = res.shape
+    if tuple(xt.shape) != tuple(res.shape) or x.weight.numel() != width:
+        raise KernelLibraryError(f"normed_add_rmsnorm: x {tuple(xt.shape)} against residual {tuple(res.shape)}")
+    out = None
+    n_out = total
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n_out = rows.numel()
+        if weight is None:
+            raise KernelLibraryError("normed_add_rmsnorm: chosen rows need the norm that follows")
+    if weight is not None:
+        _need(weight, "weight", torch.float32)
+        out = torch.empty((n_out, width), dtype=out_dtype, device=res.device)
+    check(_l.library().pb_normed_add_rmsnorm(xt.data_ptr(), x.weight.data_ptr(), x.eps, res.data_ptr(), _ptr(rows), n_out, total,
+                                             _ptr(weight), _ptr(out), dtype_code(out_dtype), width, float(eps), _stream()),
+          "normed_add_rmsnorm")
+    return out
+
+
 class PartialSums:
     """The output of a product whose K was cut into parts: ``parts`` is float32
     [n, rows, width] and the value is their sum.  The residual add takes it as
@@ -78,6 +136,18 @@ class PartialSums:
 
     def materialize(self, dtype: torch.dtype) -> torch.Tensor:
         return self.parts.sum(dim=0).to(dtype)
+
+
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """[T, 2I] (gate columns first) -> a sigmoid(alpha a) (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit); [T, I]."""
+    _need(gate_up, "gate_up")
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelLibraryError("clamped_glu: merged projection must have an even number of columns")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    check(_l.library().pb_clamped_glu(gate_up.data_ptr(), out.data_ptr(), dtype_code(gate_up.dtype), T, two_i // 2,
+                                      float(limit), float(alpha), _stream()), "clamped_glu")
+    return out
 
 
 def _x_args(x, out_dtype: torch.dtype, what: str):
@@ -339,3 +409,133 @@ def decode_advance(tokens: torch.Tensor, positions: torch.Tensor, kv_len: Option
         _need(counters, "counters", torch.int64)
     check(_l.library().pb_decode_advance(tokens.data_ptr(), positions.data_ptr(), _ptr(kv_len), _ptr(counters),
                                          sampled.data_ptr(), tokens.numel(), int(max_positions), _stream()), "decode_advance")
+
+
+def _cols(t: torch.Tensor, name: str) -> None:
+    _need(t, name, contiguous=False)
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelLibraryError(f"{name} must be [tokens, columns] with dense rows")
+
+
+def kv_write_pages(k: torch.Tensor, v: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, positions: torch.Tensor,
+                   token_row: torch.Tensor, block_table: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    """A step's keys [T, key heads * dk] and values [T, value heads * dv] (columns of a projection) into their
+    pages [pages, heads, page_size, d]: key and value heads may differ in number and size."""
+    _cols(k, "k")
+    _cols(v, "v")
+    _need(k_pages, "k_pages", k.dtype)
+    _need(v_pages, "v_pages", k.dtype)
+    _need(positions, "positions", torch.int32)
+    _need(token_row, "token_row", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    T = k.shape[0]
+    num_pages, nk, page_size, dk = k_pages.shape
+    _, nv, _, dv = v_pages.shape
+    if k.shape[1] != nk * dk or v.shape != (T, nv * dv) or v_pages.shape[0] != num_pages or v_pages.shape[2] != page_size:
+        raise KernelLibraryError(f"kv_write_pages: keys {tuple(k.shape)}, values {tuple(v.shape)} do not fit pages "
+                                 f"{tuple(k_pages.shape)}, {tuple(v_pages.shape)}")
+    check(_l.library().pb_kv_write_pages(
+        k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), dtype_code(k.dtype),
+        positions.data_ptr(), token_row.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, num_pages, T,
+        nk, dk, nv, dv, 1 if kv_swizzled(k.dtype, dk) else 0, 1 if kv_swizzled(k.dtype, dv) else 0, _ptr(status), _stream()),
+        "kv_write_pages")
+
+
+def diff_attention_ref(q: torch.Tensor, gate: Optional[torch.Tensor], k_pages: torch.Tensor, v_pages: torch.Tensor,
+                       positions: torch.Tensor, token_row: torch.Tensor, block_table: torch.Tensor, n_heads: int,
+                       scale: float, temp_coef: float, temp_every: int, lam: float, norm_eps: float, out_scale: float,
+                       window: Optional[int] = None, status: Optional[torch.Tensor] = None,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Plain differential attention: q [T, heads * 2 * dim] and gate [T, heads * vdim] (columns of a projection, gate
+    may be None) against keys [pages, 2 * kv heads, page_size, dim] and values [pages, kv heads, page_size, vdim];
+    returns [T, heads, vdim]: (map 0 - lam * map 1) at unit root mean square, times out_scale, times sigmoid(gate)."""
+    _cols(q, "q")
+    _need(k_pages, "k_pages", q.dtype)
+    _need(v_pages, "v_pages", q.dtype)
+    _need(positions, "positions", torch.int32)
+    _need(token_row, "token_row", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    T = q.shape[0]
+    num_pages, nk, page_size, dim = k_pages.shape
+    _, n_kv, _, vdim = v_pages.shape
+    if nk != 2 * n_kv or q.shape[1] != n_heads * 2 * dim or n_heads % n_kv:
+        raise KernelLibraryError(f"diff_attention: q {tuple(q.shape)} with {n_heads} heads does not fit keys {tuple(k_pages.shape)} "
+                                 f"and values {tuple(v_pages.shape)}")
+    if gate is not None:
+        _cols(gate, "gate")
+        if gate.dtype != q.dtype or tuple(gate.shape) != (T, n_heads * vdim):
+            raise KernelLibraryError(f"diff_attention: gate {tuple(gate.shape)} is not [tokens, heads * vdim]")
+    if out is None:
+        out = torch.empty((T, n_heads, vdim), dtype=q.dtype, device=q.device)
+    check(_l.library().pb_diff_attention_ref(
+        q.data_ptr(), q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, k_pages.data_ptr(), v_pages.data_ptr(),
+        out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(), token_row.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], page_size, num_pages, T, n_heads, n_kv, dim, vdim, float(scale), float(temp_coef), int(temp_every),
+        float(lam), float(norm_eps), float(out_scale), int(window) if window else 0, 1 if kv_swizzled(q.dtype, dim) else 0,
+        1 if kv_swizzled(q.dtype, vdim) else 0, _ptr(status), _stream()), "diff_attention_ref")
+    return out
+
+
+def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, group_top: int, renormalize: bool):
+    """float32 router logits [T, E] -> (experts int32 [T, top], weights float32 [T, top])."""
+    _need(logits, "logits", torch.float32)
+    T, E = logits.shape
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    check(_l.library().pb_moe_route(logits.data_ptr(), T, E, top, groups, keep, group_top, 1 if renormalize else 0,
+                                    ids.data_ptr(), weights.data_ptr(), _stream()), "moe_route")
+    return ids, weights
+
+
+class MoePlan:
+    """Where a step's (token, choice) slots sit once grouped by expert; all on the device."""
+
+    def __init__(self, offsets, order, place_of, tile_expert, tile_row0, max_tiles):
+        self.offsets, self.order, self.place_of = offsets, order, place_of
+        self.tile_expert, self.tile_row0, self.max_tiles = tile_expert, tile_row0, max_tiles
+
+
+def moe_sort(ids: torch.Tensor, n_experts: int) -> MoePlan:
+    _need(ids, "ids", torch.int32)
+    n_slots = ids.numel()
+    lib = _l.library()
+    max_tiles = -(-n_slots // lib.pb_moe_tile_rows()) + n_experts
+    ints = torch.empty(n_experts + 1 + 2 * n_slots + 2 * max_tiles, dtype=torch.int32, device=ids.device)
+    o = [0, n_experts + 1, n_experts + 1 + n_slots, n_experts + 1 + 2 * n_slots, n_experts + 1 + 2 * n_slots + max_tiles]
+    plan = MoePlan(ints[o[0]:o[1]], ints[o[1]:o[2]], ints[o[2]:o[3]], ints[o[3]:o[4]], ints[o[4]:], max_tiles)
+    check(lib.pb_moe_sort(ids.data_ptr(), n_slots, n_experts, plan.offsets.data_ptr(), plan.order.data_ptr(),
+                          plan.place_of.data_ptr(), plan.tile_expert.data_ptr(), plan.tile_row0.data_ptr(), max_tiles, _stream()),
+          "moe_sort")
+    return plan
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gated: bool, gather_div: int = 0,
+             out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The experts' products over the plan's places.  a [rows, K]; w [E, N (2 N when gated: gate rows, then up rows), K];
+    row of place p is ``order[p] // gather_div`` (the token of a slot) or, with gather_div 0, p itself.  Returns
+    [places, N]: a W_e^T, or silu(a Wg_e^T) * (a Wu_e^T)."""
+    _cols(a, "a")
+    _need(w, "w", a.dtype)
+    E, rows_w, Kdim = w.shape
+    if a.shape[1] != Kdim or (gated and rows_w % 2):
+        raise KernelLibraryError(f"moe_gemm: a {tuple(a.shape)} against w {tuple(w.shape)}")
+    N = rows_w // 2 if gated else rows_w
+    out_dtype = out_dtype or a.dtype
+    places = plan.order.numel()
+    out = torch.empty((places, N), dtype=out_dtype, device=a.device)
+    check(_l.library().pb_moe_gemm(a.data_ptr(), a.stride(0), plan.order.data_ptr() if gather_div else None, max(1, gather_div),
+                                   w.data_ptr(), w.stride(0), N, Kdim, 1 if gated else 0, plan.tile_expert.data_ptr(),
+                                   plan.tile_row0.data_ptr(), plan.offsets.data_ptr(), plan.max_tiles, out.data_ptr(), out.stride(0),
+                                   dtype_code(a.dtype), dtype_code(out_dtype), _stream()), "moe_gemm")
+    return out
+
+
+def moe_combine(y: torch.Tensor, plan: MoePlan, weights: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """out[t] = sum_c weights[t, c] * y[place of slot (t, c)], float32 sums; y float32 [places, width]."""
+    _need(y, "y", torch.float32)
+    _need(weights, "weights", torch.float32)
+    T, top = weights.shape
+    out = torch.empty((T, y.shape[1]), dtype=out_dtype, device=y.device)
+    check(_l.library().pb_moe_combine(y.data_ptr(), plan.place_of.data_ptr(), weights.data_ptr(), out.data_ptr(),
+                                      dtype_code(out_dtype), T, top, y.shape[1], _stream()), "moe_combine")
+    return out

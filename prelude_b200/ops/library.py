@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 16
+ABI_VERSION = 17
 
 
 class KernelLibraryError(RuntimeError):
@@ -58,6 +58,16 @@ _SIGNATURES = {
     "pb_gemm_stream_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, L, I, P, P], I),
     "pb_scatter_i32": ([P, L, P, P, I, P, P], I),
     "pb_decode_advance": ([P, P, P, P, P, I, I, P], I),
+    "pb_embed_sinusoid": ([P, P, P, I, P, P, I, I, I, P], I),
+    "pb_clamped_glu": ([P, P, I, I, I, F, F, P], I),
+    "pb_normed_add_rmsnorm": ([P, P, F, P, P, I, I, P, P, I, I, F, P], I),
+    "pb_kv_write_pages": ([P, L, P, L, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P], I),
+    "pb_diff_attention_ref": ([P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, F, I, F, F, F, I, I, I, P, P], I),
+    "pb_moe_route": ([P, I, I, I, I, I, I, I, P, P, P], I),
+    "pb_moe_tile_rows": ([], I),
+    "pb_moe_sort": ([P, I, I, P, P, P, P, P, I, P], I),
+    "pb_moe_gemm": ([P, L, P, I, P, L, I, I, I, P, P, P, I, P, L, I, I, P], I),
+    "pb_moe_combine": ([P, P, P, P, I, I, I, I, P], I),
 }
 
 _lock = threading.Lock()

@@ -50,3 +50,55 @@ class PreNormResidualBlock:
         a = self.mixer.forward(x, batch, cache, write_cache)
         x = self.ff_norm.add_forward(a, res)
         return self.feed_forward.forward(x)
+
+
+@register_part("block", "sandwich_residual")
+class SandwichResidualBlock:
+    """A norm before and after each sublayer:
+
+        res += delta ; a = mixer(norm1(res)) ; res += norm1b(a) ; f = ff(norm2(res)) ; return norm2b(f), pending
+
+    The norm after a sublayer and the add and norm that follow are one kernel: what this block returns is its
+    feed-forward's output with ``norm2b`` still to be applied (``kernels.Normed``), which the next block's first
+    norm, or the model's final norm, applies while it adds.  A block without a feed-forward returns its mixer's
+    output the same way.
+    """
+
+    def __init__(self, spec: BlockSpec, prefix: str = ""):
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and (spec.ff_norm is None or spec.ff_post_norm is None)):
+            raise ValueError("a sandwich block needs a norm after every sublayer it has")
+        self.spec = spec
+        p = spec.prefix
+        self.mixer_norm = make_part("norm", spec.mixer_norm, f"{p}.{spec.mixer_norm_name}")
+        self.mixer = make_part("mixer", spec.mixer, f"{p}.{spec.mixer_name}")
+        self.mixer_post_norm = make_part("norm", spec.mixer_post_norm, f"{p}.{spec.mixer_post_norm_name}")
+        self.ff_norm = self.feed_forward = self.ff_post_norm = None
+        if spec.feed_forward is not None:
+            self.ff_norm = make_part("norm", spec.ff_norm, f"{p}.{spec.ff_norm_name}")
+            self.feed_forward = make_part("feed_forward", spec.feed_forward, f"{p}.{spec.ff_name}")
+            self.ff_post_norm = make_part("norm", spec.ff_post_norm, f"{p}.{spec.ff_post_norm_name}")
+
+    def parts(self):
+        return tuple(x for x in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.ff_norm, self.feed_forward,
+                                 self.ff_post_norm) if x is not None)
+
+    def tensors(self) -> Dict[str, TensorReq]:
+        out: Dict[str, TensorReq] = {}
+        for part in self.parts():
+            out.update(part.tensors())
+        return out
+
+    def load(self, get, ctx: RunContext) -> None:
+        for part in self.parts():
+            part.load(get, ctx)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, delta, res: torch.Tensor, batch, cache, write_cache: bool):
+        x = self.mixer_norm.add_forward(delta, res)
+        a = self.mixer_post_norm.pending(self.mixer.forward(x, batch, cache, write_cache))
+        if self.feed_forward is None:
+            return a
+        x = self.ff_norm.add_forward(a, res)
+        return self.ff_post_norm.pending(self.feed_forward.forward(x))

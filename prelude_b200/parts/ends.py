@@ -14,7 +14,7 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
-from ..config.spec import LinearHeadSpec, TokenEmbeddingSpec
+from ..config.spec import LinearHeadSpec, SinusoidEmbeddingSpec, TokenEmbeddingSpec
 from ..ops import kernels as K
 from ..ops.linear import linear
 from ..weights.loader import TensorReq
@@ -35,6 +35,26 @@ class TokenEmbedding:
 
     def forward(self, batch) -> torch.Tensor:
         return K.embed_gather(batch.token_ids, self.table)
+
+
+@register_part("embedding", "token_embedding_sinusoid")
+class SinusoidTokenEmbedding(TokenEmbedding):
+    """The token's row plus a fixed position vector of sines and cosines of the token's position
+    (entry 2i: sin(p base^(-2i/hidden)), entry 2i + 1: its cosine).  The rates are made once in 64-bit; the kernel
+    takes angle, sine and cosine in 64-bit and rounds the sum once to the float32 residual stream."""
+
+    def __init__(self, spec: SinusoidEmbeddingSpec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        self.rate: Optional[torch.Tensor] = None
+
+    def load(self, get, ctx: RunContext) -> None:
+        super().load(get, ctx)
+        s = self.spec
+        i = torch.arange(0, s.hidden_size, 2, dtype=torch.float64)
+        self.rate = torch.pow(torch.tensor(float(s.base), dtype=torch.float64), -i / s.hidden_size).to(ctx.device).contiguous()
+
+    def forward(self, batch) -> torch.Tensor:
+        return K.embed_sinusoid(batch.token_ids, batch.positions, self.table, self.rate)
 
 
 @register_part("head", "linear_head")

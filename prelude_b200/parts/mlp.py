@@ -12,7 +12,7 @@ from typing import Dict
 
 import torch
 
-from ..config.spec import GatedMlpSpec
+from ..config.spec import ClampedGluSpec, GatedMlpSpec
 from ..ops import kernels as K
 from ..ops.linear import gated_linear_silu, linear
 from ..weights.loader import TensorReq
@@ -56,4 +56,38 @@ class GatedMlp:
         act = gated_linear_silu(x, self.w_gate_up) if self.spec.activation == "silu" else None
         if act is None:
             act = _ACTIVATIONS[self.spec.activation](linear(x, self.w_gate_up))
+        return linear(act, self.w_down, partial_sums_ok=True)
+
+
+@register_part("feed_forward", "clamped_glu")
+class ClampedGlu:
+    """down(a * sigmoid(alpha a) * (b + 1)) with a = min(gate(x), limit) and b = clamp(up(x), -limit, limit): gate and up
+    rows one below the other, one product, the activation kernel, the down projection."""
+
+    def __init__(self, spec: ClampedGluSpec, prefix: str):
+        self.spec, self.prefix = spec, prefix
+        self.w_gate_up = self.w_down = None
+
+    def tensors(self) -> Dict[str, TensorReq]:
+        s, p = self.spec, self.prefix
+        return {
+            f"{p}.{s.gate_name}": TensorReq((s.intermediate_size, s.hidden_size)),
+            f"{p}.{s.up_name}": TensorReq((s.intermediate_size, s.hidden_size)),
+            f"{p}.{s.down_name}": TensorReq((s.hidden_size, s.intermediate_size)),
+        }
+
+    def load(self, get, ctx: RunContext) -> None:
+        s, p = self.spec, self.prefix
+
+        def mat(name):
+            return get(f"{p}.{name}").to(device=ctx.device, dtype=ctx.dtype)
+
+        self.w_gate_up = torch.cat([mat(s.gate_name), mat(s.up_name)], dim=0).contiguous()
+        self.w_down = mat(s.down_name).contiguous()
+
+    def activation_bytes_per_token(self, elem: int) -> int:
+        return 3 * self.spec.intermediate_size * elem + 4 * self.spec.hidden_size * 4
+
+    def forward(self, x: torch.Tensor):
+        act = K.clamped_glu(linear(x, self.w_gate_up), self.spec.limit, self.spec.alpha)
         return linear(act, self.w_down, partial_sums_ok=True)

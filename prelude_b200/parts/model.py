@@ -19,8 +19,10 @@ from ..ops.linear import step_status
 from ..weights.loader import TensorReq, WeightStore
 from . import attention as _attention  # noqa: F401  (registers the part)
 from . import block as _block  # noqa: F401
+from . import diff_attention as _diff_attention  # noqa: F401
 from . import ends as _ends  # noqa: F401
 from . import mlp as _mlp  # noqa: F401
+from . import moe as _moe  # noqa: F401
 from . import norm as _norm  # noqa: F401
 from . import rope as _rope  # noqa: F401
 from .registry import KvPagesNeed, RunContext, RuntimeCaps, StateNeed, capturable, make_part
@@ -31,6 +33,13 @@ class DecoderModel:
         self.spec = spec
         self.order = spec.resolved_order()
         self.blocks = [make_part("block", b, b.prefix) for b in spec.blocks]
+        # a block that only ever reads another call's cache has no keys and values of its own; its mixer is told
+        # so before the model lists the tensors it needs
+        writes = {c.block for c in self.order if c.writes_cache}
+        for i, b in enumerate(self.blocks):
+            share = getattr(getattr(b, "mixer", None), "share_cache", None)
+            if i not in writes and callable(share):
+                share()
         self.final_norm = make_part("norm", spec.final_norm, spec.final_norm_name)
         self.embedding = make_part("embedding", spec.embedding_spec(), "")
         self.head = make_part("head", spec.head_spec(), "")

@@ -107,10 +107,25 @@ def capturable(part) -> bool:
 class KvPagesNeed:
     """A mixer that keeps keys and values of ``n_kv_heads`` x ``head_dim`` per
     token in pages; ``window`` set means only the last ``window`` tokens are
-    ever read again."""
+    ever read again.  Where the values differ from the keys in head count or
+    size, ``v_heads`` and ``v_head_dim`` say so (None: as the keys)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_heads: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_heads(self) -> int:
+        return self.n_kv_heads if self.v_heads is None else self.v_heads
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    @property
+    def elements_per_token(self) -> int:
+        return self.n_kv_heads * self.head_dim + self.value_heads * self.value_dim
 
 
 @dataclass(frozen=True)

@@ -9,7 +9,7 @@ The list of tensors comes from the model itself (``DecoderModel.tensors()``),
 so this works for any registered architecture.  Each tensor is drawn from a
 generator seeded by (seed, tensor name): the values of a tensor do not depend
 on which other tensors the model has.  Matrices and biases are N(0, std);
-norm scales are 1 + U(-jitter, jitter).
+norm scales are 1 + U(-jitter, jitter), or U(-jitter, jitter) where the model stores them around zero.
 """
 from __future__ import annotations
 
@@ -45,6 +45,10 @@ def random_tensors(config: Union[dict, object], seed: int = 0, std: float = 0.02
         g = _generator(seed, name, device)
         if req.role == "norm":
             t = 1.0 + (torch.rand(req.shape, generator=g, dtype=torch.float32, device=device) * 2.0 - 1.0) * norm_jitter
+        elif req.role == "norm_zero":       # a scale stored around zero
+            t = (torch.rand(req.shape, generator=g, dtype=torch.float32, device=device) * 2.0 - 1.0) * norm_jitter
+        elif req.role == "vector":          # a small vector whose products with its like enter an exponential
+            t = torch.randn(req.shape, generator=g, dtype=torch.float32, device=device) * (0.5 / max(1, req.shape[0]) ** 0.5)
         else:
             t = torch.randn(req.shape, generator=g, dtype=torch.float32, device=device) * std
         out[name] = t.to(dtype)
