@@ -32,7 +32,7 @@ from .spec import (BlockSpec, ClampedGluSpec, DiffAttentionSpec, LayerCall, Mode
 POSITION_BASE = 10000.0
 DENSE_SIGMOID_SLOPE = 1.702
 GROUP_SCORE_TOP = 2
-MAX_POSITIONS = 1 << 24          # positions are 32-bit floats in the position vector: exact up to here
+MAX_POSITIONS = 1 << 20          # the design names no longest sequence; this bounds tables, not the arithmetic
 
 
 def _is_int(v) -> bool:

@@ -125,7 +125,7 @@ class Engine:
         self.caps = self.model.runtime_caps()
         cuda_graph = bool(cuda_graph and self.caps.cuda_graph)
         self.cache = CacheManager(needs, page_size, int(num_pages), max_running_requests, self.device, self.dtype,
-                                  max_request_tokens=self.max_model_len if cuda_graph else None)
+                                  max_request_tokens=min(self.max_model_len, int(num_pages) * page_size) if cuda_graph else None)   # no request outgrows the pool
         self.runner = ModelRunner(self.model, self.cache)
         self.sched_config = SchedulerConfig(
             max_running_requests=max_running_requests, max_num_batched_tokens=max_num_batched_tokens,

@@ -114,7 +114,8 @@ def route(z: torch.Tensor, top: int, groups: int, keep: int):
 
 def routed_experts(x: torch.Tensor, w: Dict[str, torch.Tensor], r: dict) -> torch.Tensor:
     """Weighted sum of the chosen experts' silu-gated feed-forwards; w holds router and e<k>.gate/up/down."""
-    idx, wt = route(x @ w["router"].T, r["top"], r["groups"]["count"], r["groups"]["keep"])
+    groups = r.get("groups") or {"count": 1, "keep": 1}          # no groups named: all experts are one group
+    idx, wt = route(x @ w["router"].T, r["top"], groups["count"], groups["keep"])
     y = torch.zeros_like(x)
     for t in range(x.shape[0]):
         for e, a in zip(idx[t].tolist(), wt[t]):
