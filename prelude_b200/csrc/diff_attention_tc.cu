@@ -1,0 +1,446 @@
+// Differential attention on the tensor cores (bfloat16 operands, float32 accumulators and softmax), for prompt
+// portions and for decoded tokens.
+//
+// A block takes a tile of 64 query rows - the tokens of one request's portion times the query heads of one
+// key/value head - and walks the request's keys in tiles of 64.  It has eight warps: warps 0..3 hold score map 0 of
+// rows 16 w .. 16 w + 15, warps 4..7 score map 1 of the same rows; each is a flash-attention warp with keys of `dim`
+// and values of `vdim` (S = Q K^T and O += P V as mma.sync m16n8k16, running maximum and sum in float32, base 2).
+// Both maps read the same value tile from shared memory.  The query temperature and the scale multiply the scores in
+// float32.  The softmax weights enter the second product as a sum of two bfloat16 numbers (the weight rounded, and
+// what the rounding lost), so that the difference of two nearly equal maps does not inherit a bfloat16 rounding of
+// its weights.  At the end the warps of map 1 hand their normalised rows over through shared memory and the warps of
+// map 0 do the head's epilogue: difference, unit root mean square, scale, gate, store.
+//
+// Keys and values come from the pages with 16-byte asynchronous copies into padded rows (a permuted page is
+// straightened on the way), two tiles in flight where shared memory allows.  A row of keys beyond the request's last
+// position, or of a page that a window has given back, is filled with zeros, so that no weight of zero meets a
+// value that is not a number.
+//
+// Decoded tokens have a tile of their own (`tile_seq` null: tile i is token i).  Their keys can be cut into
+// `n_splits` ranges, one block each; the blocks then leave unnormalised sums with their maxima and the merge kernel
+// below adds them up and does the epilogue.
+#include "attention_common.cuh"
+
+struct DiffAttnParams {
+    const __nv_bfloat16* q; long long q_stride;          // [T, heads * 2 * dim]
+    const __nv_bfloat16* gate; long long gate_stride;    // [T, heads * vdim] or null
+    const __nv_bfloat16* k_pages;                        // [pages, 2 * kv heads, page_size, dim]
+    const __nv_bfloat16* v_pages;                        // [pages, kv heads, page_size, vdim]
+    __nv_bfloat16* out;                                  // [T, heads, vdim]
+    const int32_t* block_table; const int32_t* positions; const int32_t* token_row;
+    const int32_t* cu_q; const int32_t* tile_seq; const int32_t* tile_tok0;
+    float* part_o;                                       // [T, heads, 2, n_splits, vdim]
+    float* part_ml;                                      // [T, heads, 2, n_splits, 2]
+    int n_splits, stages;
+    int table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, dim, vdim, group, window;
+    int k_swizzle, v_swizzle;
+    float scale_log2, temp_coef; int temp_every;
+    float lambda, norm_eps, out_scale;
+    int* status;
+};
+
+__device__ __forceinline__ void ldsm_x4_at(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans_at(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ float da_temperature(int pos, float coef, int every) {
+    return coef == 0.f ? 1.0f : 1.0f + coef * logf((float)((pos + 1) / every + 1));
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnParams p) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t4 = lane & 3;
+    const int map = warp >> 2, row0 = (warp & 3) * 16;
+    const int g = blockIdx.y, split = blockIdx.z;
+    const int dim = p.dim, vdim = p.vdim, group = p.group;
+    const int tpt = 64 / group;
+    int tok_first, n_tok;
+    if (p.tile_seq) {
+        const int seq = p.tile_seq[blockIdx.x], tok0 = p.tile_tok0[blockIdx.x], base = p.cu_q[seq];
+        tok_first = base + tok0;
+        n_tok = min(tpt, p.cu_q[seq + 1] - base - tok0);
+    } else {
+        tok_first = blockIdx.x;
+        n_tok = 1;
+    }
+    const int trow = p.token_row[tok_first];
+    if (trow < 0) return;                                   // a padding row of a captured step
+    const int pos_first = p.positions[tok_first], pos_last = pos_first + n_tok - 1;
+    const int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int kt_lo = lo / 64, kt_hi = pos_last / 64;
+    const int per = (kt_hi - kt_lo + p.n_splits) / p.n_splits;
+    const int kt_begin = kt_lo + split * per, kt_end = min(kt_hi + 1, kt_begin + per);
+    const int32_t* table = p.block_table + (size_t)trow * p.table_stride;
+
+    const int SK = dim + 8, SV = vdim + 8;                  // elements per row in shared memory
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem);                 // [2][64][SK]
+    const size_t stage_elems = (size_t)2 * 64 * SK + (size_t)64 * SV;
+    __nv_bfloat16* stage0 = Qs + (size_t)2 * 64 * SK;                            // per stage: K [2][64][SK], V [64][SV]
+
+    // queries of both maps: row r is token r / group, head g * group + r % group
+    {
+        const int cpr = dim / 8;
+        for (int i = tid; i < 2 * 64 * cpr; i += 256) {
+            const int c = i / (64 * cpr), r = (i / cpr) % 64, ch = i % cpr;
+            const int tl = r / group, hh = r % group;
+            const bool ok = tl < n_tok;
+            const __nv_bfloat16* src = p.q + (size_t)(tok_first + (ok ? tl : 0)) * p.q_stride + (size_t)((g * group + hh) * 2 + c) * dim + ch * 8;
+            cp_async16(Qs + ((size_t)c * 64 + r) * SK + ch * 8, src, ok);
+        }
+    }
+    bool bad_page = false;
+    auto load_tile = [&](int kt, int st) {
+        __nv_bfloat16* Ks = stage0 + (size_t)st * stage_elems;
+        __nv_bfloat16* Vs = Ks + (size_t)2 * 64 * SK;
+        const int j0 = kt * 64;
+        const int kc = dim / 8, vc = vdim / 8, cpr = 2 * kc + vc;
+        for (int i = tid; i < 64 * cpr; i += 256) {
+            const int r = i / cpr, ch = i % cpr;
+            const int j = j0 + r;
+            int page = -1;
+            if (j >= lo && j <= pos_last) {
+                page = table[j / p.page_size];
+                if (page >= p.num_pages) { bad_page = true; page = -1; }
+            }
+            const bool ok = page >= 0;
+            const int in_page = j % p.page_size;
+            if (ch < 2 * kc) {
+                const int c = ch / kc, cc = ch % kc;
+                const int stored = p.k_swizzle ? (cc ^ (in_page & 7)) : cc;
+                const __nv_bfloat16* src = p.k_pages + (((size_t)(ok ? page : 0) * (2 * p.n_kv_heads) + 2 * g + c) * p.page_size + in_page) * dim + stored * 8;
+                cp_async16(Ks + ((size_t)c * 64 + r) * SK + cc * 8, src, ok);
+            } else {
+                const int cc = ch - 2 * kc;
+                const int stored = p.v_swizzle ? (cc ^ (in_page & 7)) : cc;
+                const __nv_bfloat16* src = p.v_pages + (((size_t)(ok ? page : 0) * p.n_kv_heads + g) * p.page_size + in_page) * vdim + stored * 8;
+                cp_async16(Vs + (size_t)r * SV + cc * 8, src, ok);
+            }
+        }
+    };
+
+    // this thread's two rows (gid and gid + 8 of the warp's sixteen): position and score factor
+    int row_pos[2];
+    float sc[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = row0 + gid + 8 * h, tl = r / group;
+        row_pos[h] = tl < n_tok ? pos_first + tl : -1;
+        sc[h] = p.scale_log2 * da_temperature(max(row_pos[h], 0), p.temp_coef, p.temp_every);
+    }
+    float o[2 * NV][4];
+#pragma unroll
+    for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    // per-lane byte offsets of the ldmatrix rows
+    const unsigned q_off = (unsigned)(((size_t)map * 64 + row0 + (lane & 15)) * SK + (lane >> 4) * 8) * 2;
+    const unsigned k_off = (unsigned)(((size_t)map * 64 + (lane >> 4) * 8 + (lane & 7)) * SK + ((lane >> 3) & 1) * 8) * 2;
+    const unsigned v_off = (unsigned)(((size_t)((lane >> 3) & 1) * 8 + (lane & 7)) * SV + (lane >> 4) * 8) * 2;
+    const unsigned sQ = smem_u32(Qs);
+
+    if (kt_begin < kt_end) load_tile(kt_begin, 0);
+    cp_async_commit();
+    for (int kt = kt_begin; kt < kt_end; ++kt) {
+        const int st = p.stages == 2 ? ((kt - kt_begin) & 1) : 0;
+        if (p.stages == 2 && kt + 1 < kt_end) load_tile(kt + 1, st ^ 1);
+        cp_async_commit();
+        if (p.stages == 2) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncthreads();
+        const unsigned sK = smem_u32(stage0 + (size_t)st * stage_elems);
+        const unsigned sV = sK + (unsigned)(2 * 64 * SK * 2);
+        // ---- S = Q K^T, 16 rows x 64 keys ----
+        float s[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll 2
+        for (int kk = 0; kk < dim / 16; ++kk) {
+            unsigned qa[4];
+            ldsm_x4_at(qa, sQ + q_off + kk * 32);
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                unsigned kb[4];
+                ldsm_x4_at(kb, sK + k_off + (unsigned)(n2 * 16 * SK * 2) + kk * 32);
+                mma_bf16_free(s[2 * n2], qa, kb[0], kb[1]);
+                mma_bf16_free(s[2 * n2 + 1], qa, kb[2], kb[3]);
+            }
+        }
+        // ---- scale and temperature, mask, running maximum and sum ----
+        const int j0 = kt * 64;
+        float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j0 + nt * 8 + 2 * t4 + (e & 1);
+                const int pr = row_pos[e >> 1];
+                const bool vis = j <= pr && (p.window <= 0 || j > pr - p.window);
+                s[nt][e] = vis ? s[nt][e] * sc[e >> 1] : -INFINITY;
+                rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
+            }
+        }
+        float mref[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 1));
+            rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 2));
+            const float m_new = fmaxf(m[h], rmax[h]);
+            const float corr = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new);
+            m[h] = m_new;
+            l[h] *= corr;
+            mref[h] = m_new == -INFINITY ? 0.f : m_new;
+#pragma unroll
+            for (int i = 0; i < 2 * NV; ++i) { o[i][2 * h] *= corr; o[i][2 * h + 1] *= corr; }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[nt][e] - mref[e >> 1]);
+                s[nt][e] = pv;
+                l[e >> 1] += pv;
+            }
+        }
+        // ---- O += P V, the weights as rounded part plus remainder ----
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            unsigned hi[4], lw[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float x0 = s[2 * ks + (a >> 1)][(a & 1) * 2], x1 = s[2 * ks + (a >> 1)][(a & 1) * 2 + 1];
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
+                const float2 back = __bfloat1622float2(h2);
+                hi[a] = *reinterpret_cast<const unsigned*>(&h2);
+                lw[a] = pack_bf16(x0 - back.x, x1 - back.y);
+            }
+#pragma unroll
+            for (int d2 = 0; d2 < NV; ++d2) {
+                if (d2 * 16 < vdim) {
+                    unsigned vb[4];
+                    ldsm_x4_trans_at(vb, sV + v_off + (unsigned)(ks * 16 * SV * 2) + d2 * 32);
+                    mma_bf16_free(o[2 * d2], hi, vb[0], vb[1]);
+                    mma_bf16_free(o[2 * d2 + 1], hi, vb[2], vb[3]);
+                    mma_bf16_free(o[2 * d2], lw, vb[0], vb[1]);
+                    mma_bf16_free(o[2 * d2 + 1], lw, vb[2], vb[3]);
+                }
+            }
+        }
+        __syncthreads();
+        if (p.stages != 2 && kt + 1 < kt_end) load_tile(kt + 1, 0);
+    }
+    cp_async_wait<0>();
+    if (bad_page && p.status) atomicExch(p.status, 6);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+
+    if (p.n_splits > 1) {
+        // unnormalised sums with their maximum and sum, for the merge kernel
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (row_pos[h] < 0) continue;
+            const int r = row0 + gid + 8 * h;
+            const int tok = tok_first + r / group, head = g * group + r % group;
+            const size_t at = ((((size_t)tok * p.n_heads + head) * 2 + map) * p.n_splits + split);
+            if (t4 == 0) { p.part_ml[at * 2] = m[h]; p.part_ml[at * 2 + 1] = l[h]; }
+            float* po = p.part_o + at * vdim;
+#pragma unroll
+            for (int nt = 0; nt < 2 * NV; ++nt)
+                if (nt * 8 < vdim) *reinterpret_cast<float2*>(po + nt * 8 + 2 * t4) = make_float2(o[nt][2 * h], o[nt][2 * h + 1]);
+        }
+        return;
+    }
+
+    // ---- the head's epilogue: map 1 hands over, map 0 combines ----
+    __syncthreads();                                         // everyone is done with the tiles
+    float* A2 = reinterpret_cast<float*>(smem);              // [64][vdim + 4]
+    const int SA = vdim + 4;
+    const float inv[2] = {l[0] > 0.f ? 1.0f / l[0] : 0.f, l[1] > 0.f ? 1.0f / l[1] : 0.f};
+    if (map == 1) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float* dst = A2 + (size_t)(row0 + gid + 8 * h) * SA;
+#pragma unroll
+            for (int nt = 0; nt < 2 * NV; ++nt)
+                if (nt * 8 < vdim) *reinterpret_cast<float2*>(dst + nt * 8 + 2 * t4) = make_float2(o[nt][2 * h] * inv[h], o[nt][2 * h + 1] * inv[h]);
+        }
+    }
+    __syncthreads();
+    if (map == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float* src = A2 + (size_t)(row0 + gid + 8 * h) * SA;
+            float ss = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2 * NV; ++nt) {
+                if (nt * 8 < vdim) {
+                    const float2 a2 = *reinterpret_cast<const float2*>(src + nt * 8 + 2 * t4);
+                    o[nt][2 * h] = o[nt][2 * h] * inv[h] - p.lambda * a2.x;
+                    o[nt][2 * h + 1] = o[nt][2 * h + 1] * inv[h] - p.lambda * a2.y;
+                    ss += o[nt][2 * h] * o[nt][2 * h] + o[nt][2 * h + 1] * o[nt][2 * h + 1];
+                }
+            }
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            if (row_pos[h] < 0) continue;
+            const float f = p.out_scale / sqrtf(ss / (float)vdim + p.norm_eps);
+            const int r = row0 + gid + 8 * h;
+            const int tok = tok_first + r / group, head = g * group + r % group;
+            __nv_bfloat16* dst = p.out + ((size_t)tok * p.n_heads + head) * vdim;
+            const __nv_bfloat16* gt = p.gate ? p.gate + (size_t)tok * p.gate_stride + (size_t)head * vdim : nullptr;
+#pragma unroll
+            for (int nt = 0; nt < 2 * NV; ++nt) {
+                if (nt * 8 < vdim) {
+                    const int col = nt * 8 + 2 * t4;
+                    float v0 = o[nt][2 * h] * f, v1 = o[nt][2 * h + 1] * f;
+                    if (gt) {
+                        v0 *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col])));
+                        v1 *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col + 1])));
+                    }
+                    *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(v0, v1);
+                }
+            }
+        }
+    }
+}
+
+// One warp per (token, head): the splits' sums into the two maps, then the head's epilogue.
+__global__ void diff_attention_merge_kernel(const DiffAttnParams p) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)p.n_tokens * p.n_heads) return;
+    const int tok = (int)(item / p.n_heads), head = (int)(item % p.n_heads);
+    if (p.token_row[tok] < 0) return;
+    const int vdim = p.vdim, S = p.n_splits;
+    float d[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) d[i] = 0.f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const size_t at = ((size_t)tok * p.n_heads + head) * 2 + c;
+        const float* ml = p.part_ml + at * S * 2;
+        float M = -INFINITY;
+        for (int s = 0; s < S; ++s) M = fmaxf(M, ml[2 * s]);
+        float L = 0.f;
+        for (int s = 0; s < S; ++s) L += ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - M) * ml[2 * s + 1];
+        const float invL = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int col = lane + 32 * i;
+            if (col < vdim) {
+                float a = 0.f;
+                for (int s = 0; s < S; ++s)
+                    if (ml[2 * s] != -INFINITY) a += exp2f(ml[2 * s] - M) * p.part_o[(at * S + s) * vdim + col];
+                a *= invL;
+                d[i] = c == 0 ? a : d[i] - p.lambda * a;
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += d[i] * d[i];
+    ss = pb_warp_sum(ss);
+    const float f = p.out_scale / sqrtf(ss / (float)vdim + p.norm_eps);
+    __nv_bfloat16* dst = p.out + ((size_t)tok * p.n_heads + head) * vdim;
+    const __nv_bfloat16* gt = p.gate ? p.gate + (size_t)tok * p.gate_stride + (size_t)head * vdim : nullptr;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int col = lane + 32 * i;
+        if (col < vdim) {
+            float v = d[i] * f;
+            if (gt) v *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col])));
+            dst[col] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+static size_t diff_attention_smem(int dim, int vdim, int stages) {
+    const size_t loop = ((size_t)2 * 64 * (dim + 8) + (size_t)stages * (2 * 64 * (dim + 8) + 64 * (vdim + 8))) * 2;
+    const size_t epi = (size_t)64 * (vdim + 4) * 4;
+    return loop > epi ? loop : epi;
+}
+
+// Whether the tensor-core kernel takes the shape: sizes in multiples of 16 up to 256, at most 64 query heads per
+// key/value head, projection rows whose heads start on 16-byte boundaries.
+PB_API int pb_diff_attention_tc_supported(int n_heads, int n_kv_heads, int dim, int vdim, long long q_stride) {
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads || n_heads / n_kv_heads > 64) return 0;
+    if (dim < 16 || dim > 256 || dim % 16 || vdim < 16 || vdim > 256 || vdim % 16) return 0;
+    if (q_stride % 8) return 0;
+    return 1;
+}
+
+PB_API long long pb_diff_attention_tc_scratch_floats(int n_tokens, int n_heads, int vdim, int n_splits) {
+    return n_splits > 1 ? (long long)n_tokens * n_heads * 2 * n_splits * (vdim + 2) : 0;
+}
+
+// tile_seq null: a tile per token (decoded tokens), n_tiles = n_tokens, and n_splits blocks per tile with `scratch`
+// holding pb_diff_attention_tc_scratch_floats floats; else the tiles of prompt portions (64 / group tokens each) and
+// n_splits = 1.
+PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const void* gate, long long gate_stride, const void* k_pages,
+                                     const void* v_pages, void* out, const int32_t* block_table, int table_stride,
+                                     const int32_t* positions, const int32_t* token_row, const int32_t* cu_q,
+                                     const int32_t* tile_seq, const int32_t* tile_tok0, int n_tiles, int page_size, int num_pages,
+                                     int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim, float scale, float temp_coef,
+                                     int temp_every, float lambda, float norm_eps, float out_scale, int window, int k_swizzle,
+                                     int v_swizzle, int n_splits, float* scratch, int* status, cudaStream_t stream) {
+    PB_REQUIRE(pb_diff_attention_tc_supported(n_heads, n_kv_heads, dim, vdim, q_stride), "diff_attention_tc: shape not taken "
+               "(heads %d over %d, dim %d, vdim %d, row stride %lld)", n_heads, n_kv_heads, dim, vdim, q_stride);
+    PB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0 && temp_every > 0, "diff_attention_tc: bad cache geometry or temperature step");
+    PB_REQUIRE(q && k_pages && v_pages && out && block_table && positions && token_row, "diff_attention_tc: null pointer");
+    PB_REQUIRE(pb_aligned(q, 16) && pb_aligned(k_pages, 16) && pb_aligned(v_pages, 16) && pb_aligned(out, 4),
+               "diff_attention_tc: q and the pages must be 16-byte aligned");
+    PB_REQUIRE((tile_seq == nullptr) == (tile_tok0 == nullptr) && (tile_seq == nullptr || cu_q != nullptr), "diff_attention_tc: half a plan");
+    PB_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (tile_seq == nullptr && scratch != nullptr)),
+               "diff_attention_tc: %d splits", n_splits);
+    if (n_tiles == 0) return 0;
+    DiffAttnParams p;
+    p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+    p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
+    p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages; p.out = (__nv_bfloat16*)out;
+    p.block_table = block_table; p.positions = positions; p.token_row = token_row;
+    p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_tok0 = tile_tok0;
+    p.n_splits = n_splits;
+    p.part_o = scratch;
+    p.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * 2 * n_splits * vdim : nullptr;
+    p.table_stride = table_stride; p.page_size = page_size; p.num_pages = num_pages; p.n_tokens = n_tokens;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.dim = dim; p.vdim = vdim; p.group = n_heads / n_kv_heads; p.window = window;
+    p.k_swizzle = k_swizzle; p.v_swizzle = v_swizzle;
+    p.scale_log2 = scale * 1.4426950408889634f; p.temp_coef = temp_coef; p.temp_every = temp_every;
+    p.lambda = lambda; p.norm_eps = norm_eps; p.out_scale = out_scale; p.status = status;
+    p.stages = diff_attention_smem(dim, vdim, 2) <= 200 * 1024 ? 2 : 1;
+    const size_t smem = diff_attention_smem(dim, vdim, p.stages);
+    dim3 grid(n_tiles, n_kv_heads, n_splits);
+    PB_REQUIRE(grid.y < 65536, "diff_attention_tc: too many key/value heads");
+#define DA_LAUNCH(NVT)                                                                                                     \
+    do {                                                                                                                   \
+        static bool set_##NVT = false;                                                                                     \
+        if (!set_##NVT) {                                                                                                  \
+            cudaFuncSetAttribute(diff_attention_mma_kernel<NVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
+            set_##NVT = true;                                                                                              \
+        }                                                                                                                  \
+        pb_launch(diff_attention_mma_kernel<NVT>, grid, dim3(256), smem, stream, p);                                       \
+    } while (0)
+    if (vdim <= 32) DA_LAUNCH(2);
+    else if (vdim <= 64) DA_LAUNCH(4);
+    else if (vdim <= 96) DA_LAUNCH(6);
+    else if (vdim <= 128) DA_LAUNCH(8);
+    else DA_LAUNCH(16);
+#undef DA_LAUNCH
+    PB_CHECK_LAUNCH("diff_attention_tc");
+    if (n_splits > 1) {
+        const long long items = (long long)n_tokens * n_heads;
+        pb_launch(diff_attention_merge_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, p);
+        PB_CHECK_LAUNCH("diff_attention_merge");
+    }
+    return 0;
+}

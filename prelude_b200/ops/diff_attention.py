@@ -1,24 +1,88 @@
 """Differential attention over a step's batch: picks the kernel for the type and shape.
 
-float32 always runs the plain warp-per-row kernel, and so does bfloat16 for
-shapes the tensor-core kernels do not take.  Which one ran changes the
-rounding, never what is computed.
+float32 always runs the plain warp-per-row kernel.  bfloat16 runs the
+tensor-core kernel where it takes the shape (key and value sizes in multiples
+of 16 up to 256, at most 64 query heads per key/value head) and the plain
+kernel otherwise.  Which one ran changes the rounding, never what is computed.
+
+A step of single tokens (a decode step) gives every token a tile of its own
+and cuts its keys into ranges, one block each, so that a few long requests
+still fill the device; the ranges' sums are merged by a second kernel.  A step
+with prompt portions runs the tiles of all its requests, the single tokens
+among them, in one launch.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 
 from . import kernels as K
+from . import library as _l
+from .attention import _prefill_plan, _sm_count
+from .library import check
+
+# PRELUDE_DIFF_ATTN=ref sends bfloat16 to the plain kernel as well
+KERNEL = os.environ.get("PRELUDE_DIFF_ATTN", "auto")
+
+
+def decode_splits(n_tokens: int, n_kv_heads: int, max_context: int, device) -> int:
+    """Into how many ranges a decode step cuts a token's keys: enough blocks for two per multiprocessor, no range
+    shorter than a tile of 64 keys, 32 at most."""
+    tiles = max(1, -(-int(max_context) // 64))
+    want = max(1, (2 * _sm_count(device)) // max(1, n_tokens * n_kv_heads))
+    return max(1, min(tiles, want, 32))
 
 
 def diff_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
                    group: int, spec, lam: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [T, heads * 2 * head_dim] and gate [T, heads * value_dim] (columns of the merged projection) of the batch's
-    tokens against the pages of cache group ``group``; [T, heads, value_dim] goes to ``out`` when given."""
+    tokens against the pages of cache group ``group``; [T, heads, value_dim] goes to ``out`` when given.  While a
+    step is being captured piece by piece, attention is what the pieces are cut at (its grid follows how the
+    step's tokens are spread over requests), as for the other attention kernels."""
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty((T, spec.num_heads, spec.value_dim), dtype=q.dtype, device=q.device)
+    recorder = batch.extras.get("recorder")
+    if recorder is not None and recorder.capturing:
+        recorder.run_between_pieces(lambda: diff_attention(q, gate, k_pages, v_pages, batch, group, spec, lam, out))
+        return out
     table = batch.block_tables[group]
     temp = spec.query_temperature
-    return K.diff_attention_ref(q, gate, k_pages, v_pages, batch.positions, batch.table_row_of_token, table, spec.num_heads,
-                                spec.softmax_scale, temp.coef if temp else 0.0, temp.every if temp else 1, lam, spec.norm_eps,
-                                1.0 - spec.lambda_init, spec.window, batch.status, out=out)
+    coef, every = (temp.coef, temp.every) if temp else (0.0, 1)
+    lib = _l.library()
+    if (q.dtype != torch.bfloat16 or KERNEL == "ref"
+            or not lib.pb_diff_attention_tc_supported(spec.num_heads, spec.num_kv_heads, spec.head_dim, spec.value_dim, q.stride(0))):
+        n = batch.n_real                                   # the rows after them are padding of a captured step
+        K.diff_attention_ref(q[:n], None if gate is None else gate[:n], k_pages, v_pages, batch.positions[:n],
+                             batch.table_row_of_token[:n], table, spec.num_heads, spec.softmax_scale, coef, every, lam,
+                             spec.norm_eps, 1.0 - spec.lambda_init, spec.window, batch.status, out=out[:n])
+        return out
+    num_pages, _, page_size, dim = k_pages.shape
+    vdim = v_pages.shape[3]
+    splits, scratch = 1, None
+    if batch.decode_only:
+        tile_seq = tile_tok0 = None
+        n_tiles = T
+        max_ctx = batch.max_kv_len if batch.max_kv_len else table.shape[1] * page_size
+        if spec.window:
+            max_ctx = min(max_ctx, spec.window + 64)
+        splits = decode_splits(T, spec.num_kv_heads, max_ctx, q.device)
+        if splits > 1:
+            key = ("diff_attention_scratch", T, spec.num_heads, vdim, splits)
+            scratch = batch.extras.get(key)
+            if scratch is None:
+                floats = lib.pb_diff_attention_tc_scratch_floats(T, spec.num_heads, vdim, splits)
+                scratch = batch.extras[key] = torch.empty(max(1, floats), dtype=torch.float32, device=q.device)
+    else:
+        tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, 64 // (spec.num_heads // spec.num_kv_heads), 0, None)
+    check(lib.pb_diff_attention_tc_bf16(
+        q.data_ptr(), q.stride(0), K._ptr(gate), gate.stride(0) if gate is not None else 0, k_pages.data_ptr(), v_pages.data_ptr(),
+        out.data_ptr(), table.data_ptr(), table.shape[1], batch.positions.data_ptr(), batch.table_row_of_token.data_ptr(),
+        batch.cu_q.data_ptr(), K._ptr(tile_seq), K._ptr(tile_tok0), n_tiles, page_size, num_pages, T, spec.num_heads,
+        spec.num_kv_heads, dim, vdim, float(spec.softmax_scale), float(coef), int(every), float(lam), float(spec.norm_eps),
+        float(1.0 - spec.lambda_init), int(spec.window) if spec.window else 0, 1 if K.kv_swizzled(q.dtype, dim) else 0,
+        1 if K.kv_swizzled(q.dtype, vdim) else 0, splits, K._ptr(scratch), batch.status.data_ptr(),
+        _l.current_stream_ptr(q.device)), "diff_attention_tc")
+    return out
