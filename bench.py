@@ -282,6 +282,201 @@ def time_e2e(engine, cfg, batch, steps):
             "d2h_bytes_per_step": round((st.d2h_bytes - before.d2h_bytes) / n_steps, 1), "decode_ms": decode_ms}, (t0, t1)
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --workload pabelix: the Pabelix design beside Qwen3 dense at equal layer sizes
+# ---------------------------------------------------------------------------------------------------------------
+def pabelix_config(width, heads, kv_heads, dim, vdim, ff, experts, top, expert_ff, layers, vocab):
+    """Layers that resemble a real model's: differential attention everywhere; the first layer's feed-forward dense,
+    the others routed (top * expert_ff = ff, so a token does the dense layer's work); every third layer reads the
+    keys and values of the layer before it."""
+    out = []
+    for i in range(layers):
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "diff": 0.5,
+             "q_temp": {"coef": 0.1, "every": 512}}
+        if i % 3 == 2:
+            m["kv_from"] = i - 1
+        mlp = ({"kind": "dense", "ff": ff, "limit": 7.0} if i == 0 else
+               {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}})
+        out.append({"type": "attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Pabelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
+PABELIX_SIZES = {
+    # name: (width, heads, kv heads, dim, vdim, ff, experts, top, expert ff); Qwen3 at the same width has `heads` heads of
+    # 2 * dim = vdim, the same key/value heads and the same feed-forward width
+    "2k": (2048, 16, 4, 64, 128, 8192, 32, 4, 2048),
+    "4k": (4096, 32, 8, 64, 128, 12288, 64, 6, 2048),
+}
+
+
+def _engine_for(cfg, num_pages, max_running):
+    import torch
+    from prelude_b200 import Engine
+    from prelude_b200.config import load_model_config
+    from prelude_b200.engine.loading import build_model
+    from prelude_b200.weights.loader import WeightStore
+    from prelude_b200.weights.random_init import random_tensors
+    tensors = random_tensors(cfg, seed=0, std=0.02, norm_jitter=0.05, dtype=torch.bfloat16, device="cuda:0")
+    model = build_model(load_model_config(cfg).to_model_spec(), WeightStore.from_tensors(tensors), "bf16", "cuda:0")
+    del tensors
+    torch.cuda.empty_cache()
+    return Engine(model, page_size=PAGE_SIZE, num_pages=num_pages, max_running_requests=max_running,
+                  max_num_batched_tokens=max(8192, PREFILL_TOKENS), max_model_len=CONTEXT_LEN, cuda_graph=True, cuda_graph_max_bs=64)
+
+
+def _event_ms(fn, warmup=3, reps=10, flush=None):
+    """Median device time of fn() in milliseconds, CUDA events on the launching stream; ``flush`` (a tensor larger than
+    the L2 cache) is overwritten between repetitions."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    # one launch costs the host more than a small kernel takes: replay it from a captured graph, so that the events
+    # bracket device work only
+    try:
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        fn = graph.replay
+        fn()
+    except Exception:
+        torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        if flush is not None:
+            flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    return statistics.median(times)
+
+
+def pabelix_kernels(pk, size):
+    """The new design's kernels beside their like of the closest model, one launch each, as fractions of the
+    measured peaks: prompt attention over one 2,048-token request, decode attention of 8 tokens at 2,048 keys, the
+    routed feed-forward's two grouped products beside one library product of the same work."""
+    import torch
+    from prelude_b200.cache.manager import CacheManager
+    from prelude_b200.config.spec import DiffAttentionSpec, QueryTemperatureSpec
+    from prelude_b200.engine.batch import StepItem, build_step_batch
+    from prelude_b200.ops import kernels as K
+    from prelude_b200.ops.attention import paged_attention
+    from prelude_b200.ops.diff_attention import diff_attention
+    from prelude_b200.parts.registry import KvPagesNeed
+    width, H, G, dim, vdim, ff, E, top, eff = PABELIX_SIZES[size]
+    dev = torch.device("cuda:0")
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)
+    bf = torch.bfloat16
+    out = {}
+    T, ctx, B = 2048, 2048, 8
+    spec = DiffAttentionSpec(width, H, G, dim, vdim, dim ** -0.5, 0.5, 1e-6, QueryTemperatureSpec(0.1, 512))
+    needs = [KvPagesNeed(2 * G, dim, None, G, vdim), KvPagesNeed(G, vdim)]
+    cache = CacheManager(needs, PAGE_SIZE, (B * (ctx + 16) + T) // PAGE_SIZE + 8, B + 1, dev, bf)
+    for n in (0, 1):
+        lc = cache.layer_cache(n)
+        lc.k_pages.normal_()
+        lc.v_pages.normal_()
+    # prompt attention: one request of T tokens
+    cache.add_request("p")
+    cache.grow("p", T)
+    batch = build_step_batch([StepItem("p", [0] * T, 0, [])], cache.block_tables(["p"]), [cache.slot_of("p")], dev, 10, 1 << 20)
+    proj = torch.randn(T, H * 2 * dim + H * vdim, device=dev).to(bf)
+    q, gate = proj[:, :H * 2 * dim], proj[:, H * 2 * dim:]
+    lc0, lc1 = cache.layer_cache(0), cache.layer_cache(1)
+    ms = _event_ms(lambda: diff_attention(q, gate, lc0.k_pages, lc0.v_pages, batch, cache.group_of[0], spec, 0.6), flush=flush)
+    pairs = T * (T + 1) // 2
+    flops = 2 * H * pairs * 2 * (dim + vdim)
+    out["prefill_attention"] = {"pabelix_ms": round(ms, 4), "pabelix_tflops": round(flops / ms / 1e9, 1)}
+    q3 = torch.randn(T, H, vdim, device=dev).to(bf)
+    ms = _event_ms(lambda: paged_attention(q3, lc1.k_pages, lc1.v_pages, batch, cache.group_of[1], vdim ** -0.5, None), flush=flush)
+    out["prefill_attention"].update(qwen3_ms=round(ms, 4), qwen3_tflops=round(H * pairs * 4 * vdim / ms / 1e9, 1))
+    cache.release("p")
+    # decode attention: B tokens at ctx keys
+    rids = [f"d{i}" for i in range(B)]
+    for r in rids:
+        cache.add_request(r)
+        cache.grow(r, ctx + 1)
+    batch = build_step_batch([StepItem(r, [0], ctx, []) for r in rids], cache.block_tables(rids), [cache.slot_of(r) for r in rids], dev, 10, 1 << 20)
+    proj = torch.randn(B, H * 2 * dim + H * vdim, device=dev).to(bf)
+    q, gate = proj[:, :H * 2 * dim], proj[:, H * 2 * dim:]
+    ms = _event_ms(lambda: diff_attention(q, gate, lc0.k_pages, lc0.v_pages, batch, cache.group_of[0], spec, 0.6), flush=flush, reps=20)
+    nbytes = B * (ctx + 1) * G * (2 * dim + vdim) * 2
+    out["decode_attention"] = {"pabelix_us": round(ms * 1e3, 2), "pabelix_gbs": round(nbytes / ms / 1e6, 1)}
+    q3 = torch.randn(B, H, vdim, device=dev).to(bf)
+    ms = _event_ms(lambda: paged_attention(q3, lc1.k_pages, lc1.v_pages, batch, cache.group_of[1], vdim ** -0.5, None), flush=flush, reps=20)
+    out["decode_attention"].update(qwen3_us=round(ms * 1e3, 2), qwen3_gbs=round(B * (ctx + 1) * G * 2 * vdim * 2 / ms / 1e6, 1))
+    # the routed feed-forward's products beside library products of the same work
+    for rows, name in ((T, "prefill"), (B, "decode")):
+        x = torch.randn(rows, width, device=dev).to(bf)
+        ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).to(torch.int32)
+        w1 = (torch.randn(E, 2 * eff, width, device=dev) * 0.02).to(bf)
+        w2 = (torch.randn(E, width, eff, device=dev) * 0.02).to(bf)
+        plan = K.moe_sort(ids, E)
+        h = K.moe_gemm(x, w1, plan, gated=True, gather_div=top)
+        ms1 = _event_ms(lambda: K.moe_gemm(x, w1, plan, gated=True, gather_div=top), flush=flush)
+        ms2 = _event_ms(lambda: K.moe_gemm(h, w2, plan, gated=False, out_dtype=torch.float32), flush=flush)
+        flops = 2 * rows * top * 3 * eff * width
+        d1 = (torch.randn(2 * top * eff, width, device=dev) * 0.02).to(bf)
+        d2 = (torch.randn(width, top * eff, device=dev) * 0.02).to(bf)
+        from prelude_b200.ops.linear import linear
+        hd = K.silu_mul(linear(x, d1))
+        msd = _event_ms(lambda: linear(K.silu_mul(linear(x, d1)), d2), flush=flush)
+        touched = min(E, rows * top) * 3 * eff * width * 2
+        out[f"routed_products_{name}"] = {"pabelix_ms": round(ms1 + ms2, 4), "pabelix_tflops": round(flops / (ms1 + ms2) / 1e9, 1),
+                                           "pabelix_weight_gbs": round(touched / (ms1 + ms2) / 1e6, 1),
+                                           "dense_same_work_ms": round(msd, 4), "dense_tflops": round(flops / msd / 1e9, 1),
+                                           "dense_weight_gbs": round(3 * top * eff * width * 2 / msd / 1e6, 1)}
+        del w1, w2, d1, d2
+    out["peaks"] = {"bf16_tflops": pk["bf16_tflops"], "hbm_gbs": pk["hbm_gbs"], "source": pk["source"]}
+    return out
+
+
+def pabelix_compare(args):
+    """Prefill and decode throughput of Pabelix beside Qwen3 dense at equal layer sizes (random weights, bfloat16):
+    one prompt of --prefill-tokens through the step function, and --batch requests decoding behind --prefix-len
+    tokens on the captured step, both timed on the device.  One JSON line of its own."""
+    import torch
+    pk = peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    t_begin = time.time()
+    points = []
+    vocab = 32768
+    for size in args.sizes.split(","):
+        width, H, G, dim, vdim, ff, E, top, eff = PABELIX_SIZES[size]
+        layers = args.layers or 6
+        arms = {
+            "pabelix": pabelix_config(width, H, G, dim, vdim, ff, E, top, eff, layers, vocab),
+            "qwen3": dict(QWEN3_4B, vocab_size=vocab, hidden_size=width, intermediate_size=ff, num_hidden_layers=layers,
+                          num_attention_heads=H, num_key_value_heads=G, head_dim=vdim, tie_word_embeddings=True),
+        }
+        point = {"size": size, "layers": layers, "width": width}
+        for name, cfg in arms.items():
+            pages_per_req = -(-(PREFIX_LEN + args.warmup + args.steps + 2) // PAGE_SIZE)
+            engine = _engine_for(cfg, args.batch * pages_per_req + 2 * (PREFILL_TOKENS // PAGE_SIZE) + 8, args.batch + 2)
+            shim = {"vocab_size": vocab}
+            prefill_ms, _ = time_prefill(engine, shim, args.warmup)
+            dec, _ = time_decode(engine, shim, args.batch, args.steps, args.warmup, seed=1)
+            point[name] = {"prefill_tok_s": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                           "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms_per_step"], 4),
+                           "weight_gb": round(engine.model.weight_bytes() / 1e9, 3)}
+            del engine
+            torch.cuda.empty_cache()
+        point["kernels"] = pabelix_kernels(pk, size)
+        points.append(point)
+    clocks.stop()
+    print(json.dumps({"metric": "Pabelix beside Qwen3 dense at equal layer sizes: prefill and decode tokens a second, device-timed",
+                      "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "steps": args.steps,
+                      "warmup": args.warmup, "config": {"batch": args.batch, "prefix_len": PREFIX_LEN, "prefill_tokens": PREFILL_TOKENS,
+                                                        "page_size": PAGE_SIZE, "l2": "inputs_exceed_l2 (steps), flushed (kernels)"},
+                      "points": points, "clocks": clocks.summary([(t_begin, time.time())])}))
+    return 0
+
+
 def serve(args):
     """A mixed continuous batch through ``Engine.generate`` (host tokens in, host tokens out): ``--requests`` prompts
     of uniform random ids with lengths uniform in [128, 2048], prompts cut into portions of ``--prefill-chunk``
@@ -346,8 +541,10 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels' timeline of one layer of the decode step to stderr (needs PRELUDE_TIMELINE=1 in the environment)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
-                    help="serving: a mixed continuous batch through Engine.generate instead of the decode step (a line of its own)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "pabelix"],
+                    help="serving: a mixed continuous batch through Engine.generate instead of the decode step (a line of its own); "
+                         "pabelix: the Pabelix design beside Qwen3 dense at equal layer sizes (a line of its own)")
+    ap.add_argument("--sizes", default="2k,4k", help="pabelix: which layer sizes to run (2k, 4k)")
     ap.add_argument("--requests", type=int, default=32, help="serving: number of requests")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: tokens per portion of a prompt")
     ap.add_argument("--new-tokens", type=int, default=256, help="serving: generated tokens per request")
@@ -372,6 +569,9 @@ def main():
     if args.workload == "serving":
         CONTEXT_LEN = max(CONTEXT_LEN, 2048 + args.new_tokens + 64)
         return serve(args)
+    if args.workload == "pabelix":
+        args.layers = 0 if args.layers == MODEL["num_hidden_layers"] else args.layers
+        return pabelix_compare(args)
     import torch
     pk = peaks()
     # cache: the largest point (64 requests) with room for prefix + generated tokens, in whole pages

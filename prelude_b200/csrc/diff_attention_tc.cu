@@ -32,6 +32,7 @@ struct DiffAttnParams {
     float* part_o;                                       // [T, heads, 2, n_splits, vdim]
     float* part_ml;                                      // [T, heads, 2, n_splits, 2]
     int n_splits, stages;
+    int split_weights;                                   // the softmax weights enter O += P V as rounded part plus remainder
     int table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, dim, vdim, group, window;
     int k_swizzle, v_swizzle;
     float scale_log2, temp_coef; int temp_every;
@@ -51,7 +52,8 @@ __device__ __forceinline__ float da_temperature(int pos, float coef, int every) 
     return coef == 0.f ? 1.0f : 1.0f + coef * logf((float)((pos + 1) / every + 1));
 }
 
-template <int NV>
+// NV: 16-column steps of the values at most; KS: 16-element steps of the keys (0: read from the parameters).
+template <int NV, int KS>
 __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnParams p) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t4 = lane & 3;
     const int map = warp >> 2, row0 = (warp & 3) * 16;
     const int g = blockIdx.y, split = blockIdx.z;
-    const int dim = p.dim, vdim = p.vdim, group = p.group;
+    const int dim = KS ? KS * 16 : p.dim, vdim = p.vdim, group = p.group;
     const int tpt = 64 / group;
     int tok_first, n_tok;
     if (p.tile_seq) {
@@ -84,44 +86,41 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
     const size_t stage_elems = (size_t)2 * 64 * SK + (size_t)64 * SV;
     __nv_bfloat16* stage0 = Qs + (size_t)2 * 64 * SK;                            // per stage: K [2][64][SK], V [64][SV]
 
+    // Four threads share a row of every 64-row tile (queries, keys, values) and take its 16-byte pieces in turn.
+    const int lrow = tid >> 2, lsub = tid & 3;
     // queries of both maps: row r is token r / group, head g * group + r % group
     {
-        const int cpr = dim / 8;
-        for (int i = tid; i < 2 * 64 * cpr; i += 256) {
-            const int c = i / (64 * cpr), r = (i / cpr) % 64, ch = i % cpr;
-            const int tl = r / group, hh = r % group;
-            const bool ok = tl < n_tok;
-            const __nv_bfloat16* src = p.q + (size_t)(tok_first + (ok ? tl : 0)) * p.q_stride + (size_t)((g * group + hh) * 2 + c) * dim + ch * 8;
-            cp_async16(Qs + ((size_t)c * 64 + r) * SK + ch * 8, src, ok);
+        const int tl = lrow / group, hh = lrow % group;
+        const bool ok = tl < n_tok;
+        const __nv_bfloat16* src = p.q + (size_t)(tok_first + (ok ? tl : 0)) * p.q_stride + (size_t)((g * group + hh) * 2) * dim;
+        for (int cc = lsub; cc < 2 * (dim / 8); cc += 4) {
+            const int c = cc >= dim / 8 ? 1 : 0, ch = cc - c * (dim / 8);
+            cp_async16(Qs + ((size_t)c * 64 + lrow) * SK + ch * 8, src + cc * 8, ok);
         }
     }
     bool bad_page = false;
     auto load_tile = [&](int kt, int st) {
         __nv_bfloat16* Ks = stage0 + (size_t)st * stage_elems;
         __nv_bfloat16* Vs = Ks + (size_t)2 * 64 * SK;
-        const int j0 = kt * 64;
-        const int kc = dim / 8, vc = vdim / 8, cpr = 2 * kc + vc;
-        for (int i = tid; i < 64 * cpr; i += 256) {
-            const int r = i / cpr, ch = i % cpr;
-            const int j = j0 + r;
-            int page = -1;
-            if (j >= lo && j <= pos_last) {
-                page = table[j / p.page_size];
-                if (page >= p.num_pages) { bad_page = true; page = -1; }
-            }
-            const bool ok = page >= 0;
-            const int in_page = j % p.page_size;
-            if (ch < 2 * kc) {
-                const int c = ch / kc, cc = ch % kc;
-                const int stored = p.k_swizzle ? (cc ^ (in_page & 7)) : cc;
-                const __nv_bfloat16* src = p.k_pages + (((size_t)(ok ? page : 0) * (2 * p.n_kv_heads) + 2 * g + c) * p.page_size + in_page) * dim + stored * 8;
-                cp_async16(Ks + ((size_t)c * 64 + r) * SK + cc * 8, src, ok);
-            } else {
-                const int cc = ch - 2 * kc;
-                const int stored = p.v_swizzle ? (cc ^ (in_page & 7)) : cc;
-                const __nv_bfloat16* src = p.v_pages + (((size_t)(ok ? page : 0) * p.n_kv_heads + g) * p.page_size + in_page) * vdim + stored * 8;
-                cp_async16(Vs + (size_t)r * SV + cc * 8, src, ok);
-            }
+        const int j = kt * 64 + lrow;
+        int page = -1;
+        if (j >= lo && j <= pos_last) {
+            page = table[j / p.page_size];
+            if (page >= p.num_pages) { bad_page = true; page = -1; }
+        }
+        const bool ok = page >= 0;
+        const int in_page = j % p.page_size, x = in_page & 7;
+        const __nv_bfloat16* k0 = p.k_pages + (((size_t)(ok ? page : 0) * (2 * p.n_kv_heads) + 2 * g) * p.page_size + in_page) * dim;
+        const __nv_bfloat16* k1 = k0 + (size_t)p.page_size * dim;
+        const __nv_bfloat16* v0 = p.v_pages + (((size_t)(ok ? page : 0) * p.n_kv_heads + g) * p.page_size + in_page) * vdim;
+        for (int cc = lsub; cc < dim / 8; cc += 4) {
+            const int stored = p.k_swizzle ? (cc ^ x) : cc;
+            cp_async16(Ks + (size_t)lrow * SK + cc * 8, k0 + stored * 8, ok);
+            cp_async16(Ks + ((size_t)64 + lrow) * SK + cc * 8, k1 + stored * 8, ok);
+        }
+        for (int cc = lsub; cc < vdim / 8; cc += 4) {
+            const int stored = p.v_swizzle ? (cc ^ x) : cc;
+            cp_async16(Vs + (size_t)lrow * SV + cc * 8, v0 + stored * 8, ok);
         }
     };
 
@@ -134,6 +133,10 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
         row_pos[h] = tl < n_tok ? pos_first + tl : -1;
         sc[h] = p.scale_log2 * da_temperature(max(row_pos[h], 0), p.temp_coef, p.temp_every);
     }
+    // a warp whose sixteen rows hold no token (a decoded token fills few rows of its tile) copies and waits with the
+    // others and computes nothing
+    const bool warp_active = row0 / group < n_tok;
+    const bool rows_missing = 64 / group * group < 64 || n_tok < 64 / group;
     float o[2 * NV][4];
 #pragma unroll
     for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -155,12 +158,14 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
         __syncthreads();
         const unsigned sK = smem_u32(stage0 + (size_t)st * stage_elems);
         const unsigned sV = sK + (unsigned)(2 * 64 * SK * 2);
+        if (warp_active) {
         // ---- S = Q K^T, 16 rows x 64 keys ----
         float s[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll 2
-        for (int kk = 0; kk < dim / 16; ++kk) {
+#pragma unroll
+        for (int kk = 0; kk < (KS ? KS : 16); ++kk) {
+            if (KS == 0 && kk >= dim / 16) break;
             unsigned qa[4];
             ldsm_x4_at(qa, sQ + q_off + kk * 32);
 #pragma unroll
@@ -171,18 +176,22 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
                 mma_bf16_free(s[2 * n2 + 1], qa, kb[2], kb[3]);
             }
         }
-        // ---- scale and temperature, mask, running maximum and sum ----
+        // ---- scale and temperature, mask (only in tiles that hold a key some row may not see), running maximum ----
         const int j0 = kt * 64;
+        const bool edge = rows_missing || j0 + 63 > pos_first || (p.window > 0 && j0 <= pos_last - p.window);
         float rmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int j = j0 + nt * 8 + 2 * t4 + (e & 1);
-                const int pr = row_pos[e >> 1];
-                const bool vis = j <= pr && (p.window <= 0 || j > pr - p.window);
-                s[nt][e] = vis ? s[nt][e] * sc[e >> 1] : -INFINITY;
-                rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
+                float v = s[nt][e] * sc[e >> 1];
+                if (edge) {
+                    const int j = j0 + nt * 8 + 2 * t4 + (e & 1);
+                    const int pr = row_pos[e >> 1];
+                    v = (j <= pr && (p.window <= 0 || j > pr - p.window)) ? v : -INFINITY;
+                }
+                s[nt][e] = v;
+                rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
             }
         }
         float mref[2];
@@ -191,18 +200,20 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
             rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 1));
             rmax[h] = fmaxf(rmax[h], __shfl_xor_sync(0xffffffffu, rmax[h], 2));
             const float m_new = fmaxf(m[h], rmax[h]);
-            const float corr = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new);
-            m[h] = m_new;
-            l[h] *= corr;
             mref[h] = m_new == -INFINITY ? 0.f : m_new;
+            if (m_new > m[h]) {                              // the maximum grew: earlier sums shrink
+                const float corr = (m[h] == -INFINITY) ? 0.f : ex2_approx(m[h] - m_new);
+                m[h] = m_new;
+                l[h] *= corr;
 #pragma unroll
-            for (int i = 0; i < 2 * NV; ++i) { o[i][2 * h] *= corr; o[i][2 * h + 1] *= corr; }
+                for (int i = 0; i < 2 * NV; ++i) { o[i][2 * h] *= corr; o[i][2 * h + 1] *= corr; }
+            }
         }
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float pv = exp2f(s[nt][e] - mref[e >> 1]);
+                const float pv = ex2_approx(s[nt][e] - mref[e >> 1]);
                 s[nt][e] = pv;
                 l[e >> 1] += pv;
             }
@@ -226,10 +237,13 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
                     ldsm_x4_trans_at(vb, sV + v_off + (unsigned)(ks * 16 * SV * 2) + d2 * 32);
                     mma_bf16_free(o[2 * d2], hi, vb[0], vb[1]);
                     mma_bf16_free(o[2 * d2 + 1], hi, vb[2], vb[3]);
-                    mma_bf16_free(o[2 * d2], lw, vb[0], vb[1]);
-                    mma_bf16_free(o[2 * d2 + 1], lw, vb[2], vb[3]);
+                    if (p.split_weights) {
+                        mma_bf16_free(o[2 * d2], lw, vb[0], vb[1]);
+                        mma_bf16_free(o[2 * d2 + 1], lw, vb[2], vb[3]);
+                    }
                 }
             }
+        }
         }
         __syncthreads();
         if (p.stages != 2 && kt + 1 < kt_end) load_tile(kt + 1, 0);
@@ -392,7 +406,7 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
                                      const int32_t* tile_seq, const int32_t* tile_tok0, int n_tiles, int page_size, int num_pages,
                                      int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim, float scale, float temp_coef,
                                      int temp_every, float lambda, float norm_eps, float out_scale, int window, int k_swizzle,
-                                     int v_swizzle, int n_splits, float* scratch, int* status, cudaStream_t stream) {
+                                     int v_swizzle, int n_splits, int split_weights, float* scratch, int* status, cudaStream_t stream) {
     PB_REQUIRE(pb_diff_attention_tc_supported(n_heads, n_kv_heads, dim, vdim, q_stride), "diff_attention_tc: shape not taken "
                "(heads %d over %d, dim %d, vdim %d, row stride %lld)", n_heads, n_kv_heads, dim, vdim, q_stride);
     PB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0 && temp_every > 0, "diff_attention_tc: bad cache geometry or temperature step");
@@ -410,6 +424,7 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
     p.block_table = block_table; p.positions = positions; p.token_row = token_row;
     p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_tok0 = tile_tok0;
     p.n_splits = n_splits;
+    p.split_weights = split_weights;
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * 2 * n_splits * vdim : nullptr;
     p.table_stride = table_stride; p.page_size = page_size; p.num_pages = num_pages; p.n_tokens = n_tokens;
@@ -421,20 +436,27 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
     const size_t smem = diff_attention_smem(dim, vdim, p.stages);
     dim3 grid(n_tiles, n_kv_heads, n_splits);
     PB_REQUIRE(grid.y < 65536, "diff_attention_tc: too many key/value heads");
-#define DA_LAUNCH(NVT)                                                                                                     \
-    do {                                                                                                                   \
-        static bool set_##NVT = false;                                                                                     \
-        if (!set_##NVT) {                                                                                                  \
-            cudaFuncSetAttribute(diff_attention_mma_kernel<NVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
-            set_##NVT = true;                                                                                              \
-        }                                                                                                                  \
-        pb_launch(diff_attention_mma_kernel<NVT>, grid, dim3(256), smem, stream, p);                                       \
+#define DA_LAUNCH_K(NVT, KST)                                                                                                    \
+    do {                                                                                                                         \
+        static bool set_##NVT##_##KST = false;                                                                                   \
+        if (!set_##NVT##_##KST) {                                                                                                \
+            cudaFuncSetAttribute(diff_attention_mma_kernel<NVT, KST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);  \
+            set_##NVT##_##KST = true;                                                                                            \
+        }                                                                                                                        \
+        pb_launch(diff_attention_mma_kernel<NVT, KST>, grid, dim3(256), smem, stream, p);                                        \
+    } while (0)
+#define DA_LAUNCH(NVT)                          \
+    do {                                        \
+        if (dim == 64) DA_LAUNCH_K(NVT, 4);     \
+        else if (dim == 128) DA_LAUNCH_K(NVT, 8); \
+        else DA_LAUNCH_K(NVT, 0);               \
     } while (0)
     if (vdim <= 32) DA_LAUNCH(2);
     else if (vdim <= 64) DA_LAUNCH(4);
     else if (vdim <= 96) DA_LAUNCH(6);
     else if (vdim <= 128) DA_LAUNCH(8);
     else DA_LAUNCH(16);
+#undef DA_LAUNCH_K
 #undef DA_LAUNCH
     PB_CHECK_LAUNCH("diff_attention_tc");
     if (n_splits > 1) {

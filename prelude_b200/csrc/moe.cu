@@ -21,6 +21,7 @@
 #include <mma.h>
 
 #define MOE_BM 64
+#define MOE_BM_LARGE 128
 #define MOE_BN 64
 #define MOE_BK 16
 #define MOE_MAX_TOP 32
@@ -113,7 +114,7 @@ PB_API int pb_moe_route(const float* logits, int n_tokens, int n_experts, int to
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t* __restrict__ ids, int n_slots, int n_experts,
                                                         int32_t* __restrict__ offsets, int32_t* __restrict__ order,
                                                         int32_t* __restrict__ place_of, int32_t* __restrict__ tile_expert,
-                                                        int32_t* __restrict__ tile_row0, int max_tiles) {
+                                                        int32_t* __restrict__ tile_row0, int max_tiles, int tile_rows) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS + 1], tile0[MOE_MAX_EXPERTS + 1];
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t* __restric
             start[e] = at;
             tile0[e] = tiles;
             at += count[e];
-            tiles += (count[e] + MOE_BM - 1) / MOE_BM;
+            tiles += (count[e] + tile_rows - 1) / tile_rows;
         }
         start[n_experts] = at;
         tile0[n_experts] = tiles;
@@ -141,7 +142,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t* __restric
         for (int k = 0, n = tile0[e + 1] - tile0[e]; k < n; ++k) {
             if (tile0[e] + k < max_tiles) {
                 tile_expert[tile0[e] + k] = e;
-                tile_row0[tile0[e] + k] = start[e] + k * MOE_BM;
+                tile_row0[tile0[e] + k] = start[e] + k * tile_rows;
             }
         }
         count[e] = 0;                                       // now the cursor of the expert's places
@@ -159,15 +160,17 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t* __restric
     }
 }
 
-PB_API int pb_moe_tile_rows() { return MOE_BM; }
+// Rows of a tile: 128 where the experts have many rows each (prompt steps: the large-tile kernel), else 64.
+PB_API int pb_moe_tile_rows(int n_slots, int n_experts) { return n_slots >= 48 * n_experts ? MOE_BM_LARGE : MOE_BM; }
 
 PB_API int pb_moe_sort(const int32_t* ids, int n_slots, int n_experts, int32_t* offsets, int32_t* order, int32_t* place_of,
-                       int32_t* tile_expert, int32_t* tile_row0, int max_tiles, cudaStream_t stream) {
+                       int32_t* tile_expert, int32_t* tile_row0, int max_tiles, int tile_rows, cudaStream_t stream) {
     PB_REQUIRE(n_slots >= 0 && n_experts > 0 && n_experts <= MOE_MAX_EXPERTS, "moe_sort: bad sizes slots=%d E=%d", n_slots, n_experts);
-    PB_REQUIRE(max_tiles >= (n_slots + MOE_BM - 1) / MOE_BM + n_experts, "moe_sort: room for %d tiles is too little", max_tiles);
+    PB_REQUIRE(tile_rows == MOE_BM || tile_rows == MOE_BM_LARGE, "moe_sort: tiles have %d or %d rows", MOE_BM, MOE_BM_LARGE);
+    PB_REQUIRE(max_tiles >= (n_slots + tile_rows - 1) / tile_rows + n_experts, "moe_sort: room for %d tiles is too little", max_tiles);
     PB_REQUIRE(ids && offsets && order && place_of && tile_expert && tile_row0, "moe_sort: null pointer");
     pb_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, ids, n_slots, n_experts, offsets, order, place_of, tile_expert,
-              tile_row0, max_tiles);
+              tile_row0, max_tiles, tile_rows);
     PB_CHECK_LAUNCH("moe_sort");
     return 0;
 }
@@ -338,11 +341,144 @@ __global__ void __launch_bounds__(256) moe_gemm_bf16_kernel(const __nv_bfloat16*
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The products of prompt steps, where an expert has rows by the hundred: tiles of 128 rows x 128 weight rows (gated:
+// 64 gate rows and the 64 up rows of the same features), K in steps of 64 through a three-stage ring of asynchronous
+// 16-byte copies, eight warps of 64 x 32 each (gated: 16 gate and the matching 16 up columns, so that a thread holds
+// both factors of its outputs), operands by ldmatrix, mma.sync m16n8k16.  Needs K % 8 == 0.
+// ---------------------------------------------------------------------------------------------------------------
+#define MOE_LK 64
+#define MOE_LS (MOE_LK + 8)
+#define MOE_LSTAGES 3
+#define MOE_LARGE_SMEM (MOE_LSTAGES * 2 * 128 * MOE_LS * 2)
+
+__device__ __forceinline__ void moe_cp16(void* smem, const void* gmem, bool pred) {
+    unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    int n = pred ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(sa), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void moe_ldsm4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void moe_mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TC, bool GATED>
+__global__ void __launch_bounds__(256) moe_gemm_large_kernel(const __nv_bfloat16* __restrict__ A, long long lda,
+                                                             const int32_t* __restrict__ order, int a_div,
+                                                             const __nv_bfloat16* __restrict__ W, long long w_expert_stride, int N,
+                                                             int K, const int32_t* __restrict__ tile_expert,
+                                                             const int32_t* __restrict__ tile_row0,
+                                                             const int32_t* __restrict__ offsets, TC* __restrict__ C, long long ldc) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int row0 = tile_row0[blockIdx.x], row_end = offsets[e + 1];
+    constexpr int BN = GATED ? 64 : 128;                      // output columns of a tile
+    const int n0 = blockIdx.y * BN;
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(moe_smem);                 // [stages][128][MOE_LS]
+    __nv_bfloat16* Bs = As + MOE_LSTAGES * 128 * MOE_LS;                             // [stages][128][MOE_LS]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t4 = lane & 3;
+    const __nv_bfloat16* We = W + (size_t)e * w_expert_stride;
+    // this thread's 16-byte pieces of every 128 x MOE_LK operand tile: piece tid % CPR of rows tid / CPR + n * (256 / CPR)
+    constexpr int CPR = MOE_LK / 8, RPP = 256 / CPR, NP = 128 / RPP;
+    const int lr = tid / CPR, lc = (tid % CPR) * 8;
+    const __nv_bfloat16* a_src[NP];
+    const __nv_bfloat16* b_src[NP];
+    bool a_ok[NP], b_ok[NP];
+#pragma unroll
+    for (int n = 0; n < NP; ++n) {
+        const int r = lr + RPP * n;
+        const int pl = row0 + r;
+        const int src = pl < row_end ? (order ? order[pl] / a_div : pl) : -1;
+        a_ok[n] = src >= 0;
+        a_src[n] = A + (size_t)(src >= 0 ? src : 0) * lda + lc;
+        const int col = GATED ? n0 + (r & 63) : n0 + r;
+        b_ok[n] = col < N;
+        b_src[n] = We + (size_t)((GATED && r >= 64 ? N : 0) + (b_ok[n] ? col : 0)) * K + lc;
+    }
+    auto load = [&](int st, int k0) {
+        const bool kin = k0 + lc < K;
+#pragma unroll
+        for (int n = 0; n < NP; ++n) {
+            moe_cp16(As + ((size_t)st * 128 + lr + RPP * n) * MOE_LS + lc, a_src[n] + k0, a_ok[n] && kin);
+            moe_cp16(Bs + ((size_t)st * 128 + lr + RPP * n) * MOE_LS + lc, b_src[n] + k0, b_ok[n] && kin);
+        }
+    };
+    const int wm = warp >> 2, wn = warp & 3;
+    float acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    const unsigned sA = (unsigned)__cvta_generic_to_shared(As), sB = (unsigned)__cvta_generic_to_shared(Bs);
+    const unsigned a_off = (unsigned)((wm * 64 + (lane & 15)) * MOE_LS + (lane >> 4) * 8) * 2;
+    unsigned b_off[2];
+#pragma unroll
+    for (int nj = 0; nj < 2; ++nj) {
+        const int base = GATED ? nj * 64 + wn * 16 : wn * 32 + nj * 16;
+        b_off[nj] = (unsigned)((base + (lane >> 4) * 8 + (lane & 7)) * MOE_LS + ((lane >> 3) & 1) * 8) * 2;
+    }
+    const int KT = (K + MOE_LK - 1) / MOE_LK;
+#pragma unroll
+    for (int s0 = 0; s0 < MOE_LSTAGES - 1; ++s0) {
+        if (s0 < KT) load(s0, s0 * MOE_LK);
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
+    for (int kt = 0; kt < KT; ++kt) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(MOE_LSTAGES - 2));
+        __syncthreads();
+        if (kt + MOE_LSTAGES - 1 < KT) load((kt + MOE_LSTAGES - 1) % MOE_LSTAGES, (kt + MOE_LSTAGES - 1) * MOE_LK);
+        asm volatile("cp.async.commit_group;\n" ::);
+        const unsigned stA = sA + (unsigned)((kt % MOE_LSTAGES) * 128 * MOE_LS * 2), stB = sB + (unsigned)((kt % MOE_LSTAGES) * 128 * MOE_LS * 2);
+#pragma unroll
+        for (int kk = 0; kk < MOE_LK / 16; ++kk) {
+            unsigned a[4][4], b[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi) moe_ldsm4(a[mi], stA + a_off + (unsigned)(mi * 16 * MOE_LS * 2) + kk * 32);
+#pragma unroll
+            for (int nj = 0; nj < 2; ++nj) moe_ldsm4(b[nj], stB + b_off[nj] + kk * 32);
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) moe_mma(acc[mi][nt], a[mi], b[nt >> 1][(nt & 1) * 2], b[nt >> 1][(nt & 1) * 2 + 1]);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int pl = row0 + wm * 64 + mi * 16 + gid + 8 * h;
+            if (pl >= row_end) continue;
+            TC* crow = C + (size_t)pl * ldc;
+#pragma unroll
+            for (int nt = 0; nt < (GATED ? 2 : 4); ++nt) {
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int col = n0 + (GATED ? wn * 16 : wn * 32) + nt * 8 + 2 * t4 + q;
+                    if (col >= N) continue;
+                    float v = acc[mi][nt][2 * h + q];
+                    if (GATED) v = v / (1.0f + expf(-v)) * acc[mi][nt + (GATED ? 2 : 0)][2 * h + q];
+                    pb_st(crow + col, v);
+                }
+            }
+        }
+    }
+}
+
 // A [*, K] with row stride lda; order null or int32 [places]; W [E, (2) N, K] dense, w_expert_stride elements from one
 // expert to the next; C [places, N] with row stride ldc, of type out_dtype (float32 or the input's).  grid: max_tiles.
 PB_API int pb_moe_gemm(const void* A, long long lda, const int32_t* order, int a_div, const void* W, long long w_expert_stride,
                        int N, int K, int gated, const int32_t* tile_expert, const int32_t* tile_row0, const int32_t* offsets,
-                       int max_tiles, void* C, long long ldc, int dtype, int out_dtype, cudaStream_t stream) {
+                       int max_tiles, int tile_rows, void* C, long long ldc, int dtype, int out_dtype, cudaStream_t stream) {
+    PB_REQUIRE(tile_rows == MOE_BM || tile_rows == MOE_BM_LARGE, "moe_gemm: tiles have %d or %d rows", MOE_BM, MOE_BM_LARGE);
     PB_REQUIRE(N > 0 && K > 0 && max_tiles >= 0 && a_div > 0, "moe_gemm: bad sizes N=%d K=%d", N, K);
     PB_REQUIRE(lda >= K && ldc >= N && w_expert_stride >= (long long)(gated ? 2 : 1) * N * K, "moe_gemm: a stride is shorter than its row");
     PB_REQUIRE(A && W && C && tile_expert && tile_row0 && offsets, "moe_gemm: null pointer");
@@ -358,7 +494,23 @@ PB_API int pb_moe_gemm(const void* A, long long lda, const int32_t* order, int a
         else MOE_LAUNCH((moe_gemm_fma_kernel<float, float, false>), float, float, 0);
     } else if (dtype == PB_BF16) {
         const bool tc = K % 8 == 0 && lda % 8 == 0 && w_expert_stride % 8 == 0 && pb_aligned(A, 16) && pb_aligned(W, 16);
-        if (tc) {
+        PB_REQUIRE(tc || tile_rows == MOE_BM, "moe_gemm: tiles of %d rows need K in multiples of 8 and aligned operands", MOE_BM_LARGE);
+        if (tile_rows == MOE_BM_LARGE) {
+            grid.y = (N + (gated ? 64 : 128) - 1) / (gated ? 64 : 128);
+#define MOE_LARGE(TCC, G)                                                                                                          \
+    do {                                                                                                                           \
+        static bool set_ = false;                                                                                                  \
+        if (!set_) {                                                                                                               \
+            cudaFuncSetAttribute(moe_gemm_large_kernel<TCC, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_LARGE_SMEM);      \
+            set_ = true;                                                                                                           \
+        }                                                                                                                          \
+        pb_launch(moe_gemm_large_kernel<TCC, G>, grid, dim3(256), (size_t)MOE_LARGE_SMEM, stream, (const __nv_bfloat16*)A, lda, order, a_div, \
+                  (const __nv_bfloat16*)W, w_expert_stride, N, K, tile_expert, tile_row0, offsets, (TCC*)C, ldc);                  \
+    } while (0)
+            if (out_dtype == PB_F32) { if (gated) MOE_LARGE(float, true); else MOE_LARGE(float, false); }
+            else { if (gated) MOE_LARGE(__nv_bfloat16, true); else MOE_LARGE(__nv_bfloat16, false); }
+#undef MOE_LARGE
+        } else if (tc) {
             if (out_dtype == PB_F32) {
                 if (gated) MOE_LAUNCH((moe_gemm_bf16_kernel<float, true>), __nv_bfloat16, float, 1);
                 else MOE_LAUNCH((moe_gemm_bf16_kernel<float, false>), __nv_bfloat16, float, 0);

@@ -25,6 +25,12 @@ from .library import check
 
 # PRELUDE_DIFF_ATTN=ref sends bfloat16 to the plain kernel as well
 KERNEL = os.environ.get("PRELUDE_DIFF_ATTN", "auto")
+# Whether the softmax weights (computed in float32) enter the second product as one bfloat16 number, as in the
+# framework's other attention kernels, or as a rounded part plus what the rounding lost (PRELUDE_DIFF_ATTN_SPLIT=1:
+# two bfloat16 numbers, 16 bits of the weight, twice the tensor-core work of that product).  Measured against
+# 64-bit logits the two differ by less than a twentieth of the error that the bfloat16 queries, keys and values
+# cause, so the single number is the default.
+SPLIT_WEIGHTS = os.environ.get("PRELUDE_DIFF_ATTN_SPLIT", "0") == "1"
 
 
 def decode_splits(n_tokens: int, n_kv_heads: int, max_context: int, device) -> int:
@@ -83,6 +89,6 @@ def diff_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pages: torch
         batch.cu_q.data_ptr(), K._ptr(tile_seq), K._ptr(tile_tok0), n_tiles, page_size, num_pages, T, spec.num_heads,
         spec.num_kv_heads, dim, vdim, float(spec.softmax_scale), float(coef), int(every), float(lam), float(spec.norm_eps),
         float(1.0 - spec.lambda_init), int(spec.window) if spec.window else 0, 1 if K.kv_swizzled(q.dtype, dim) else 0,
-        1 if K.kv_swizzled(q.dtype, vdim) else 0, splits, K._ptr(scratch), batch.status.data_ptr(),
+        1 if K.kv_swizzled(q.dtype, vdim) else 0, splits, 1 if SPLIT_WEIGHTS else 0, K._ptr(scratch), batch.status.data_ptr(),
         _l.current_stream_ptr(q.device)), "diff_attention_tc")
     return out

@@ -490,21 +490,24 @@ def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, group_top:
 class MoePlan:
     """Where a step's (token, choice) slots sit once grouped by expert; all on the device."""
 
-    def __init__(self, offsets, order, place_of, tile_expert, tile_row0, max_tiles):
+    def __init__(self, offsets, order, place_of, tile_expert, tile_row0, max_tiles, tile_rows):
         self.offsets, self.order, self.place_of = offsets, order, place_of
-        self.tile_expert, self.tile_row0, self.max_tiles = tile_expert, tile_row0, max_tiles
+        self.tile_expert, self.tile_row0, self.max_tiles, self.tile_rows = tile_expert, tile_row0, max_tiles, tile_rows
 
 
-def moe_sort(ids: torch.Tensor, n_experts: int) -> MoePlan:
+def moe_sort(ids: torch.Tensor, n_experts: int, tile_rows: Optional[int] = None) -> MoePlan:
+    """Group the slots by expert.  ``tile_rows`` (64 or 128; default: the library's choice by rows per expert) is the
+    height of the row tiles the products then run on."""
     _need(ids, "ids", torch.int32)
     n_slots = ids.numel()
     lib = _l.library()
-    max_tiles = -(-n_slots // lib.pb_moe_tile_rows()) + n_experts
+    tile_rows = tile_rows or lib.pb_moe_tile_rows(n_slots, n_experts)
+    max_tiles = -(-n_slots // tile_rows) + n_experts
     ints = torch.empty(n_experts + 1 + 2 * n_slots + 2 * max_tiles, dtype=torch.int32, device=ids.device)
     o = [0, n_experts + 1, n_experts + 1 + n_slots, n_experts + 1 + 2 * n_slots, n_experts + 1 + 2 * n_slots + max_tiles]
-    plan = MoePlan(ints[o[0]:o[1]], ints[o[1]:o[2]], ints[o[2]:o[3]], ints[o[3]:o[4]], ints[o[4]:], max_tiles)
+    plan = MoePlan(ints[o[0]:o[1]], ints[o[1]:o[2]], ints[o[2]:o[3]], ints[o[3]:o[4]], ints[o[4]:], max_tiles, tile_rows)
     check(lib.pb_moe_sort(ids.data_ptr(), n_slots, n_experts, plan.offsets.data_ptr(), plan.order.data_ptr(),
-                          plan.place_of.data_ptr(), plan.tile_expert.data_ptr(), plan.tile_row0.data_ptr(), max_tiles, _stream()),
+                          plan.place_of.data_ptr(), plan.tile_expert.data_ptr(), plan.tile_row0.data_ptr(), max_tiles, tile_rows, _stream()),
           "moe_sort")
     return plan
 
@@ -521,11 +524,13 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gated: bool, gathe
         raise KernelLibraryError(f"moe_gemm: a {tuple(a.shape)} against w {tuple(w.shape)}")
     N = rows_w // 2 if gated else rows_w
     out_dtype = out_dtype or a.dtype
+    if plan.tile_rows != 64 and (a.dtype != torch.bfloat16 or Kdim % 8 or a.stride(0) % 8 or a.data_ptr() % 16):
+        raise KernelLibraryError("moe_gemm: a plan of 128-row tiles is for bfloat16 operands with K in multiples of 8")
     places = plan.order.numel()
     out = torch.empty((places, N), dtype=out_dtype, device=a.device)
     check(_l.library().pb_moe_gemm(a.data_ptr(), a.stride(0), plan.order.data_ptr() if gather_div else None, max(1, gather_div),
                                    w.data_ptr(), w.stride(0), N, Kdim, 1 if gated else 0, plan.tile_expert.data_ptr(),
-                                   plan.tile_row0.data_ptr(), plan.offsets.data_ptr(), plan.max_tiles, out.data_ptr(), out.stride(0),
+                                   plan.tile_row0.data_ptr(), plan.offsets.data_ptr(), plan.max_tiles, plan.tile_rows, out.data_ptr(), out.stride(0),
                                    dtype_code(a.dtype), dtype_code(out_dtype), _stream()), "moe_gemm")
     return out
 

@@ -37,10 +37,11 @@ from .registry import KvPagesNeed, RunContext, register_part
 
 @register_part("mixer", "diff_attention")
 class DiffAttention:
-    # set by the block: a layer that reads another layer's cache has no key and value tensors
     def __init__(self, spec: DiffAttentionSpec, prefix: str):
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError(f"{spec.num_heads} query heads do not divide over {spec.num_kv_heads} key/value heads")
+        if not (0 < spec.head_dim <= 256 and 0 < spec.value_dim <= 256):
+            raise ValueError(f"differential attention: key size {spec.head_dim} and value size {spec.value_dim} must lie in 1..256")
         self.spec, self.prefix = spec, prefix
         self.q_cols = spec.num_heads * 2 * spec.head_dim
         self.k_cols = spec.num_kv_heads * 2 * spec.head_dim

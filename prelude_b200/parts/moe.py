@@ -73,7 +73,9 @@ class RoutedExperts:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         s = self.spec
         ids, weights = self.route(x)
-        plan = K.moe_sort(ids, s.n_experts)
+        # tiles of 128 rows where the experts have many rows each and the tensor-core kernel takes the shapes, else of 64
+        small = x.dtype != torch.bfloat16 or s.hidden_size % 8 or s.expert_size % 8
+        plan = K.moe_sort(ids, s.n_experts, 64 if small else None)
         h = K.moe_gemm(x, self.w_gate_up, plan, gated=True, gather_div=s.top_k)
         y = K.moe_gemm(h, self.w_down, plan, gated=False, out_dtype=torch.float32)
         return K.moe_combine(y, plan, weights, x.dtype)

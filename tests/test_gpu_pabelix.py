@@ -341,3 +341,54 @@ def test_trace_replay_of_a_pabelix_folder(folders, tmp_path):
     b = np.fromfile(out / "2.f32", dtype="<f4").reshape(1, -1)
     for row, pos in ((a[0], 0), (a[1], 10), (b[0], 29)):
         assert float(np.abs(row - ref[pos].numpy()).max()) < 2e-4 * float(ref[pos].abs().max())
+
+
+# -- the tensor-core attention kernel against the plain kernel -----------------------------------------------------------
+@pytest.mark.parametrize("heads,kv,dim,vdim,page,window", [(8, 2, 64, 128, 16, None), (4, 4, 48, 96, 16, None), (16, 2, 128, 64, 32, None),
+                                                        (6, 2, 32, 32, 8, 100), (2, 1, 256, 256, 64, None), (4, 1, 16, 240, 16, 33)])
+def test_tensor_core_attention_equals_the_plain_kernel(heads, kv, dim, vdim, page, window):
+    """Random keys and values in scattered pages; requests of unequal length: long portions, a portion of two tokens,
+    single tokens far into a long context (their keys cut into ranges), with and without a window; then a step of
+    single tokens only.  Both kernels read the same pages."""
+    from prelude_b200.cache.manager import CacheManager
+    from prelude_b200.config.spec import DiffAttentionSpec, QueryTemperatureSpec
+    from prelude_b200.engine.batch import StepItem, build_step_batch
+    from prelude_b200.ops import diff_attention as D
+    from prelude_b200.ops import kernels as K
+    from prelude_b200.parts.registry import KvPagesNeed
+    dev = torch.device(DEV)
+    g = torch.Generator().manual_seed(heads * 31 + dim)
+    spec = DiffAttentionSpec(64, heads, kv, dim, vdim, 1.0 / math.sqrt(dim), 0.3, 1e-6, QueryTemperatureSpec(0.4, 64), window=window)
+    # (tokens already in the cache, tokens of this step)
+    mixed = [(0, 150), (700, 2), (1500, 1), (130, 70), (63, 1)]
+    decode = [(1900, 1), (5, 1), (640, 1)]
+    for shape in (mixed, decode):
+        total = sum(a + b for a, b in shape)
+        cache = CacheManager([KvPagesNeed(2 * kv, dim, None, kv, vdim)], page, sum(-(-(a + b) // page) for a, b in shape) + 3, 8, dev, torch.bfloat16)
+        items, slots = [], []
+        for i, (have, new) in enumerate(shape):
+            cache.add_request(i)
+            cache.grow(i, have + new)
+            items.append(StepItem(i, [0] * new, have, []))
+            slots.append(cache.slot_of(i))
+            # what earlier steps left: keys and values of the first `have` positions
+            if have:
+                fill = build_step_batch([StepItem(i, [0] * have, 0, [])], cache.block_tables([i]), [slots[-1]], dev, 10, 1 << 20)
+                K.kv_write_pages((torch.randn(have, 2 * kv * dim, generator=g)).to(dev, torch.bfloat16),
+                                 torch.randn(have, kv * vdim, generator=g).to(dev, torch.bfloat16), cache.layer_cache(0).k_pages,
+                                 cache.layer_cache(0).v_pages, fill.positions, fill.table_row_of_token, fill.block_tables[0])
+        batch = build_step_batch(items, cache.block_tables(list(range(len(shape)))), slots, dev, 10, 1 << 20)
+        T = batch.n_tokens
+        lc = cache.layer_cache(0)
+        K.kv_write_pages(torch.randn(T, 2 * kv * dim, generator=g).to(dev, torch.bfloat16), torch.randn(T, kv * vdim, generator=g).to(dev, torch.bfloat16),
+                         lc.k_pages, lc.v_pages, batch.positions, batch.table_row_of_token, batch.block_tables[0])
+        proj = torch.randn(T, heads * 2 * dim + heads * vdim, generator=g).to(dev, torch.bfloat16)
+        q, gate = proj[:, :heads * 2 * dim], proj[:, heads * 2 * dim:]
+        got = D.diff_attention(q, gate, lc.k_pages, lc.v_pages, batch, 0, spec, 0.8).float()
+        want = K.diff_attention_ref(q, gate, lc.k_pages, lc.v_pages, batch.positions, batch.table_row_of_token, batch.block_tables[0], heads,
+                                    spec.softmax_scale, 0.4, 64, 0.8, 1e-6, 0.7, window, batch.status).float()
+        assert int(batch.status.item()) == 0
+        assert bool(D._l.library().pb_diff_attention_tc_supported(heads, kv, dim, vdim, q.stride(0)))
+        err = (got - want).abs()
+        assert float(err.max()) < 4e-2 * float(want.abs().max()) and float(err.mean()) < 4e-3 * float(want.abs().max()), \
+            (float(err.max()), float(err.mean()), float(want.abs().max()))
