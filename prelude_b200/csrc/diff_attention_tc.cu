@@ -179,7 +179,10 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
         // ---- scale and temperature, mask (only in tiles that hold a key some row may not see), running maximum ----
         const int j0 = kt * 64;
         const bool edge = rows_missing || j0 + 63 > pos_first || (p.window > 0 && j0 <= pos_last - p.window);
-        float rmax[2] = {-INFINITY, -INFINITY};
+        // four partial maxima (and, below, sums) per row instead of one chain of sixteen
+        float pm[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) pm[h][0] = pm[h][1] = pm[h][2] = pm[h][3] = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
@@ -191,9 +194,12 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
                     v = (j <= pr && (p.window <= 0 || j > pr - p.window)) ? v : -INFINITY;
                 }
                 s[nt][e] = v;
-                rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
+                pm[e >> 1][(nt & 1) * 2 + (e & 1)] = fmaxf(pm[e >> 1][(nt & 1) * 2 + (e & 1)], v);
             }
         }
+        float rmax[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) rmax[h] = fmaxf(fmaxf(pm[h][0], pm[h][1]), fmaxf(pm[h][2], pm[h][3]));
         float mref[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -209,15 +215,20 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
                 for (int i = 0; i < 2 * NV; ++i) { o[i][2 * h] *= corr; o[i][2 * h + 1] *= corr; }
             }
         }
+        float ps[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) ps[h][0] = ps[h][1] = ps[h][2] = ps[h][3] = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float pv = ex2_approx(s[nt][e] - mref[e >> 1]);
                 s[nt][e] = pv;
-                l[e >> 1] += pv;
+                ps[e >> 1][(nt & 1) * 2 + (e & 1)] += pv;
             }
         }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) l[h] += (ps[h][0] + ps[h][1]) + (ps[h][2] + ps[h][3]);
         // ---- O += P V, the weights as rounded part plus remainder ----
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
@@ -326,43 +337,57 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
     }
 }
 
-// One warp per (token, head): the splits' sums into the two maps, then the head's epilogue.
-__global__ void diff_attention_merge_kernel(const DiffAttnParams p) {
+// A block of two warps per (token, head), warp c on map c: lane s takes split s's maximum and sum (at most 32 splits),
+// the warp agrees on the common maximum and on each split's share, and every lane adds up its columns with the splits'
+// loads independent of one another.  Map 1 goes through shared memory to warp 0, which does the head's epilogue.
+__global__ void __launch_bounds__(64) diff_attention_merge_kernel(const DiffAttnParams p) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long item = (long long)blockIdx.x * 4 + warp;
-    if (item >= (long long)p.n_tokens * p.n_heads) return;
-    const int tok = (int)(item / p.n_heads), head = (int)(item % p.n_heads);
+    __shared__ float other[256];
+    const int c = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok = blockIdx.x / p.n_heads, head = blockIdx.x % p.n_heads;
     if (p.token_row[tok] < 0) return;
     const int vdim = p.vdim, S = p.n_splits;
-    float d[8];
+    const size_t at = ((size_t)tok * p.n_heads + head) * 2 + c;
+    float ms = -INFINITY, ls = 0.f;
+    if (lane < S) { ms = p.part_ml[(at * S + lane) * 2]; ls = p.part_ml[(at * S + lane) * 2 + 1]; }
+    const float M = pb_warp_max(ms);
+    const float ws = ms == -INFINITY ? 0.f : exp2f(ms - M);
+    const float L = pb_warp_sum(ws * ls);
+    const float share = L > 0.f ? ws / L : 0.f;               // of split `lane`
+    float a[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) d[i] = 0.f;
+    for (int i = 0; i < 8; ++i) a[i] = 0.f;
+    const float* po = p.part_o + at * S * vdim;
+    for (int s0 = 0; s0 < S; s0 += 4) {
+        float v[4][8], w[4];
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-        const size_t at = ((size_t)tok * p.n_heads + head) * 2 + c;
-        const float* ml = p.part_ml + at * S * 2;
-        float M = -INFINITY;
-        for (int s = 0; s < S; ++s) M = fmaxf(M, ml[2 * s]);
-        float L = 0.f;
-        for (int s = 0; s < S; ++s) L += ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - M) * ml[2 * s + 1];
-        const float invL = L > 0.f ? 1.0f / L : 0.f;
+        for (int u = 0; u < 4; ++u) {
+            w[u] = __shfl_sync(0xffffffffu, share, min(s0 + u, 31));
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int col = lane + 32 * i;
-            if (col < vdim) {
-                float a = 0.f;
-                for (int s = 0; s < S; ++s)
-                    if (ml[2 * s] != -INFINITY) a += exp2f(ml[2 * s] - M) * p.part_o[(at * S + s) * vdim + col];
-                a *= invL;
-                d[i] = c == 0 ? a : d[i] - p.lambda * a;
+            for (int i = 0; i < 8; ++i) {
+                const int col = lane + 32 * i;
+                v[u][i] = (s0 + u < S && col < vdim) ? po[(size_t)(s0 + u) * vdim + col] : 0.f;
             }
         }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] = fmaf(s0 + u < S ? w[u] : 0.f, v[u][i], a[i]);
     }
+    if (c == 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) other[lane + 32 * i] = a[i];
+    }
+    __syncthreads();
+    if (c == 1) return;
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ss += d[i] * d[i];
+    for (int i = 0; i < 8; ++i) {
+        const int col = lane + 32 * i;
+        a[i] = col < vdim ? a[i] - p.lambda * other[col] : 0.f;
+        ss += a[i] * a[i];
+    }
     ss = pb_warp_sum(ss);
     const float f = p.out_scale / sqrtf(ss / (float)vdim + p.norm_eps);
     __nv_bfloat16* dst = p.out + ((size_t)tok * p.n_heads + head) * vdim;
@@ -371,7 +396,7 @@ __global__ void diff_attention_merge_kernel(const DiffAttnParams p) {
     for (int i = 0; i < 8; ++i) {
         const int col = lane + 32 * i;
         if (col < vdim) {
-            float v = d[i] * f;
+            float v = a[i] * f;
             if (gt) v *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col])));
             dst[col] = __float2bfloat16_rn(v);
         }
@@ -414,7 +439,7 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
     PB_REQUIRE(pb_aligned(q, 16) && pb_aligned(k_pages, 16) && pb_aligned(v_pages, 16) && pb_aligned(out, 4),
                "diff_attention_tc: q and the pages must be 16-byte aligned");
     PB_REQUIRE((tile_seq == nullptr) == (tile_tok0 == nullptr) && (tile_seq == nullptr || cu_q != nullptr), "diff_attention_tc: half a plan");
-    PB_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (tile_seq == nullptr && scratch != nullptr)),
+    PB_REQUIRE(n_splits >= 1 && n_splits <= 32 && (n_splits == 1 || (tile_seq == nullptr && scratch != nullptr)),
                "diff_attention_tc: %d splits", n_splits);
     if (n_tiles == 0) return 0;
     DiffAttnParams p;
@@ -432,7 +457,8 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
     p.k_swizzle = k_swizzle; p.v_swizzle = v_swizzle;
     p.scale_log2 = scale * 1.4426950408889634f; p.temp_coef = temp_coef; p.temp_every = temp_every;
     p.lambda = lambda; p.norm_eps = norm_eps; p.out_scale = out_scale; p.status = status;
-    p.stages = diff_attention_smem(dim, vdim, 2) <= 200 * 1024 ? 2 : 1;
+    // a decoded token's range is a tile or two: one stage, so that twice as many blocks fit a multiprocessor
+    p.stages = (n_splits == 1 && diff_attention_smem(dim, vdim, 2) <= 200 * 1024) ? 2 : 1;
     const size_t smem = diff_attention_smem(dim, vdim, p.stages);
     dim3 grid(n_tiles, n_kv_heads, n_splits);
     PB_REQUIRE(grid.y < 65536, "diff_attention_tc: too many key/value heads");
@@ -461,7 +487,8 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
     PB_CHECK_LAUNCH("diff_attention_tc");
     if (n_splits > 1) {
         const long long items = (long long)n_tokens * n_heads;
-        pb_launch(diff_attention_merge_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, p);
+        PB_REQUIRE(items < (1ll << 31), "diff_attention_tc: too many rows");
+        pb_launch(diff_attention_merge_kernel, dim3((unsigned)items), dim3(64), 0, stream, p);
         PB_CHECK_LAUNCH("diff_attention_merge");
     }
     return 0;

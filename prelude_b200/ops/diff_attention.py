@@ -34,10 +34,10 @@ SPLIT_WEIGHTS = os.environ.get("PRELUDE_DIFF_ATTN_SPLIT", "0") == "1"
 
 
 def decode_splits(n_tokens: int, n_kv_heads: int, max_context: int, device) -> int:
-    """Into how many ranges a decode step cuts a token's keys: enough blocks for two per multiprocessor, no range
+    """Into how many ranges a decode step cuts a token's keys: enough blocks for four per multiprocessor, no range
     shorter than a tile of 64 keys, 32 at most."""
     tiles = max(1, -(-int(max_context) // 64))
-    want = max(1, (2 * _sm_count(device)) // max(1, n_tokens * n_kv_heads))
+    want = max(1, (4 * _sm_count(device)) // max(1, n_tokens * n_kv_heads))
     return max(1, min(tiles, want, 32))
 
 
