@@ -32,6 +32,7 @@ struct DiffAttnParams {
     float* part_o;                                       // [T, heads, 2, n_splits, vdim]
     float* part_ml;                                      // [T, heads, 2, n_splits, 2]
     int n_splits, stages;
+    int n_parts;                                         // partial sums per (token, head, map) that the merge kernel adds up
     int split_weights;                                   // the softmax weights enter O += P V as rounded part plus remainder
     int table_stride, page_size, num_pages, n_tokens, n_heads, n_kv_heads, dim, vdim, group, window;
     int k_swizzle, v_swizzle;
@@ -53,13 +54,18 @@ __device__ __forceinline__ float da_temperature(int pos, float coef, int every) 
 }
 
 // NV: 16-column steps of the values at most; KS: 16-element steps of the keys (0: read from the parameters).
-template <int NV, int KS>
+// DEC: a decoded token's tile, whose rows (the query heads of one key/value head, sixteen at most) fit one warp: the
+// four warps of a map then share every 64-key tile, sixteen keys each, and leave four partial sums per key range,
+// which the merge kernel takes as four ranges more.  A single warp walking whole tiles is bound by the latency of
+// its own instructions (17 cycles between two of them, measured) and four of them by a quarter of it.
+template <int NV, int KS, bool DEC>
 __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnParams p) {
+    constexpr int NT = DEC ? 2 : 8;                         // 8-key score tiles per warp and key tile
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t4 = lane & 3;
-    const int map = warp >> 2, row0 = (warp & 3) * 16;
+    const int map = warp >> 2, row0 = DEC ? 0 : (warp & 3) * 16, key_off = DEC ? (warp & 3) * 16 : 0;
     const int g = blockIdx.y, split = blockIdx.z;
     const int dim = KS ? KS * 16 : p.dim, vdim = p.vdim, group = p.group;
     const int tpt = 64 / group;
@@ -135,7 +141,7 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
     }
     // a warp whose sixteen rows hold no token (a decoded token fills few rows of its tile) copies and waits with the
     // others and computes nothing
-    const bool warp_active = row0 / group < n_tok;
+    const bool warp_active = DEC || row0 / group < n_tok;
     const bool rows_missing = 64 / group * group < 64 || n_tok < 64 / group;
     float o[2 * NV][4];
 #pragma unroll
@@ -144,8 +150,8 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
 
     // per-lane byte offsets of the ldmatrix rows
     const unsigned q_off = (unsigned)(((size_t)map * 64 + row0 + (lane & 15)) * SK + (lane >> 4) * 8) * 2;
-    const unsigned k_off = (unsigned)(((size_t)map * 64 + (lane >> 4) * 8 + (lane & 7)) * SK + ((lane >> 3) & 1) * 8) * 2;
-    const unsigned v_off = (unsigned)(((size_t)((lane >> 3) & 1) * 8 + (lane & 7)) * SV + (lane >> 4) * 8) * 2;
+    const unsigned k_off = (unsigned)(((size_t)map * 64 + key_off + (lane >> 4) * 8 + (lane & 7)) * SK + ((lane >> 3) & 1) * 8) * 2;
+    const unsigned v_off = (unsigned)(((size_t)key_off + ((lane >> 3) & 1) * 8 + (lane & 7)) * SV + (lane >> 4) * 8) * 2;
     const unsigned sQ = smem_u32(Qs);
 
     if (kt_begin < kt_end) load_tile(kt_begin, 0);
@@ -160,16 +166,16 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
         const unsigned sV = sK + (unsigned)(2 * 64 * SK * 2);
         if (warp_active) {
         // ---- S = Q K^T, 16 rows x 64 keys ----
-        float s[8][4];
+        float s[NT][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < (KS ? KS : 16); ++kk) {
             if (KS == 0 && kk >= dim / 16) break;
             unsigned qa[4];
             ldsm_x4_at(qa, sQ + q_off + kk * 32);
 #pragma unroll
-            for (int n2 = 0; n2 < 4; ++n2) {
+            for (int n2 = 0; n2 < NT / 2; ++n2) {
                 unsigned kb[4];
                 ldsm_x4_at(kb, sK + k_off + (unsigned)(n2 * 16 * SK * 2) + kk * 32);
                 mma_bf16_free(s[2 * n2], qa, kb[0], kb[1]);
@@ -184,12 +190,12 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
 #pragma unroll
         for (int h = 0; h < 2; ++h) pm[h][0] = pm[h][1] = pm[h][2] = pm[h][3] = -INFINITY;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float v = s[nt][e] * sc[e >> 1];
                 if (edge) {
-                    const int j = j0 + nt * 8 + 2 * t4 + (e & 1);
+                    const int j = j0 + key_off + nt * 8 + 2 * t4 + (e & 1);
                     const int pr = row_pos[e >> 1];
                     v = (j <= pr && (p.window <= 0 || j > pr - p.window)) ? v : -INFINITY;
                 }
@@ -219,7 +225,7 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
 #pragma unroll
         for (int h = 0; h < 2; ++h) ps[h][0] = ps[h][1] = ps[h][2] = ps[h][3] = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float pv = ex2_approx(s[nt][e] - mref[e >> 1]);
@@ -231,7 +237,7 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
         for (int h = 0; h < 2; ++h) l[h] += (ps[h][0] + ps[h][1]) + (ps[h][2] + ps[h][3]);
         // ---- O += P V, the weights as rounded part plus remainder ----
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
+        for (int ks = 0; ks < NT / 2; ++ks) {
             unsigned hi[4], lw[4];
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
@@ -267,14 +273,15 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
     }
 
-    if (p.n_splits > 1) {
+    if (DEC || p.n_splits > 1) {
         // unnormalised sums with their maximum and sum, for the merge kernel
+        const int n_parts = DEC ? 4 * p.n_splits : p.n_splits, part = DEC ? 4 * split + (warp & 3) : split;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             if (row_pos[h] < 0) continue;
             const int r = row0 + gid + 8 * h;
             const int tok = tok_first + r / group, head = g * group + r % group;
-            const size_t at = ((((size_t)tok * p.n_heads + head) * 2 + map) * p.n_splits + split);
+            const size_t at = ((((size_t)tok * p.n_heads + head) * 2 + map) * n_parts + part);
             if (t4 == 0) { p.part_ml[at * 2] = m[h]; p.part_ml[at * 2 + 1] = l[h]; }
             float* po = p.part_o + at * vdim;
 #pragma unroll
@@ -347,7 +354,7 @@ __global__ void __launch_bounds__(64) diff_attention_merge_kernel(const DiffAttn
     const int c = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok = blockIdx.x / p.n_heads, head = blockIdx.x % p.n_heads;
     if (p.token_row[tok] < 0) return;
-    const int vdim = p.vdim, S = p.n_splits;
+    const int vdim = p.vdim, S = p.n_parts;
     const size_t at = ((size_t)tok * p.n_heads + head) * 2 + c;
     float ms = -INFINITY, ls = 0.f;
     if (lane < S) { ms = p.part_ml[(at * S + lane) * 2]; ls = p.part_ml[(at * S + lane) * 2 + 1]; }
@@ -418,8 +425,15 @@ PB_API int pb_diff_attention_tc_supported(int n_heads, int n_kv_heads, int dim, 
     return 1;
 }
 
-PB_API long long pb_diff_attention_tc_scratch_floats(int n_tokens, int n_heads, int vdim, int n_splits) {
-    return n_splits > 1 ? (long long)n_tokens * n_heads * 2 * n_splits * (vdim + 2) : 0;
+// Partial sums a decode step leaves per (token, head, map) when its keys are cut into n_splits ranges: with sixteen query
+// heads per key/value head at most, the four warps of a map leave one each per range.
+static int diff_attention_parts(int n_heads, int n_kv_heads, int n_splits) { return n_heads / n_kv_heads <= 16 ? 4 * n_splits : n_splits; }
+
+PB_API int pb_diff_attention_tc_max_splits(int n_heads, int n_kv_heads) { return n_heads / n_kv_heads <= 16 ? 8 : 32; }
+
+PB_API long long pb_diff_attention_tc_scratch_floats(int n_tokens, int n_heads, int n_kv_heads, int vdim, int n_splits) {
+    const int parts = diff_attention_parts(n_heads, n_kv_heads, n_splits);
+    return parts > 1 ? (long long)n_tokens * n_heads * 2 * parts * (vdim + 2) : 0;
 }
 
 // tile_seq null: a tile per token (decoded tokens), n_tiles = n_tokens, and n_splits blocks per tile with `scratch`
@@ -439,8 +453,10 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
     PB_REQUIRE(pb_aligned(q, 16) && pb_aligned(k_pages, 16) && pb_aligned(v_pages, 16) && pb_aligned(out, 4),
                "diff_attention_tc: q and the pages must be 16-byte aligned");
     PB_REQUIRE((tile_seq == nullptr) == (tile_tok0 == nullptr) && (tile_seq == nullptr || cu_q != nullptr), "diff_attention_tc: half a plan");
-    PB_REQUIRE(n_splits >= 1 && n_splits <= 32 && (n_splits == 1 || (tile_seq == nullptr && scratch != nullptr)),
-               "diff_attention_tc: %d splits", n_splits);
+    const bool dec = tile_seq == nullptr && n_heads / n_kv_heads <= 16;       // decoded tokens whose rows fit one warp
+    const int n_parts = dec ? diff_attention_parts(n_heads, n_kv_heads, n_splits) : n_splits;
+    PB_REQUIRE(n_splits >= 1 && n_parts <= 32 && (n_parts == 1 || (tile_seq == nullptr && scratch != nullptr)),
+               "diff_attention_tc: %d key ranges, %d partial sums", n_splits, n_parts);
     if (n_tiles == 0) return 0;
     DiffAttnParams p;
     p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
@@ -451,31 +467,32 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
     p.n_splits = n_splits;
     p.split_weights = split_weights;
     p.part_o = scratch;
-    p.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * 2 * n_splits * vdim : nullptr;
+    p.n_parts = n_parts;
+    p.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * 2 * n_parts * vdim : nullptr;
     p.table_stride = table_stride; p.page_size = page_size; p.num_pages = num_pages; p.n_tokens = n_tokens;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.dim = dim; p.vdim = vdim; p.group = n_heads / n_kv_heads; p.window = window;
     p.k_swizzle = k_swizzle; p.v_swizzle = v_swizzle;
     p.scale_log2 = scale * 1.4426950408889634f; p.temp_coef = temp_coef; p.temp_every = temp_every;
     p.lambda = lambda; p.norm_eps = norm_eps; p.out_scale = out_scale; p.status = status;
-    // a decoded token's range is a tile or two: one stage, so that twice as many blocks fit a multiprocessor
-    p.stages = (n_splits == 1 && diff_attention_smem(dim, vdim, 2) <= 200 * 1024) ? 2 : 1;
+    p.stages = diff_attention_smem(dim, vdim, 2) <= 200 * 1024 ? 2 : 1;
     const size_t smem = diff_attention_smem(dim, vdim, p.stages);
     dim3 grid(n_tiles, n_kv_heads, n_splits);
     PB_REQUIRE(grid.y < 65536, "diff_attention_tc: too many key/value heads");
-#define DA_LAUNCH_K(NVT, KST)                                                                                                    \
+#define DA_LAUNCH_K(NVT, KST, DECT)                                                                                              \
     do {                                                                                                                         \
-        static bool set_##NVT##_##KST = false;                                                                                   \
-        if (!set_##NVT##_##KST) {                                                                                                \
-            cudaFuncSetAttribute(diff_attention_mma_kernel<NVT, KST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);  \
-            set_##NVT##_##KST = true;                                                                                            \
+        static bool set_##NVT##_##KST##_##DECT = false;                                                                          \
+        if (!set_##NVT##_##KST##_##DECT) {                                                                                       \
+            cudaFuncSetAttribute(diff_attention_mma_kernel<NVT, KST, DECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
+            set_##NVT##_##KST##_##DECT = true;                                                                                   \
         }                                                                                                                        \
-        pb_launch(diff_attention_mma_kernel<NVT, KST>, grid, dim3(256), smem, stream, p);                                        \
+        pb_launch(diff_attention_mma_kernel<NVT, KST, DECT>, grid, dim3(256), smem, stream, p);                                  \
     } while (0)
-#define DA_LAUNCH(NVT)                          \
-    do {                                        \
-        if (dim == 64) DA_LAUNCH_K(NVT, 4);     \
-        else if (dim == 128) DA_LAUNCH_K(NVT, 8); \
-        else DA_LAUNCH_K(NVT, 0);               \
+#define DA_LAUNCH(NVT)                                 \
+    do {                                               \
+        if (dec) DA_LAUNCH_K(NVT, 0, true);            \
+        else if (dim == 64) DA_LAUNCH_K(NVT, 4, false); \
+        else if (dim == 128) DA_LAUNCH_K(NVT, 8, false); \
+        else DA_LAUNCH_K(NVT, 0, false);               \
     } while (0)
     if (vdim <= 32) DA_LAUNCH(2);
     else if (vdim <= 64) DA_LAUNCH(4);
@@ -485,7 +502,7 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
 #undef DA_LAUNCH_K
 #undef DA_LAUNCH
     PB_CHECK_LAUNCH("diff_attention_tc");
-    if (n_splits > 1) {
+    if (n_parts > 1) {
         const long long items = (long long)n_tokens * n_heads;
         PB_REQUIRE(items < (1ll << 31), "diff_attention_tc: too many rows");
         pb_launch(diff_attention_merge_kernel, dim3((unsigned)items), dim3(64), 0, stream, p);

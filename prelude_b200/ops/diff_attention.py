@@ -33,12 +33,12 @@ KERNEL = os.environ.get("PRELUDE_DIFF_ATTN", "auto")
 SPLIT_WEIGHTS = os.environ.get("PRELUDE_DIFF_ATTN_SPLIT", "0") == "1"
 
 
-def decode_splits(n_tokens: int, n_kv_heads: int, max_context: int, device) -> int:
-    """Into how many ranges a decode step cuts a token's keys: enough blocks for four per multiprocessor, no range
-    shorter than a tile of 64 keys, 32 at most."""
+def decode_splits(n_tokens: int, n_kv_heads: int, max_context: int, device, most: int = 32) -> int:
+    """Into how many ranges a decode step cuts a token's keys: enough blocks for two per multiprocessor, no range
+    shorter than a tile of 64 keys, ``most`` at most (what the merge kernel takes)."""
     tiles = max(1, -(-int(max_context) // 64))
-    want = max(1, (4 * _sm_count(device)) // max(1, n_tokens * n_kv_heads))
-    return max(1, min(tiles, want, 32))
+    want = max(1, (2 * _sm_count(device)) // max(1, n_tokens * n_kv_heads))
+    return max(1, min(tiles, want, most))
 
 
 def diff_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
@@ -74,13 +74,14 @@ def diff_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pages: torch
         max_ctx = batch.max_kv_len if batch.max_kv_len else table.shape[1] * page_size
         if spec.window:
             max_ctx = min(max_ctx, spec.window + 64)
-        splits = decode_splits(T, spec.num_kv_heads, max_ctx, q.device)
-        if splits > 1:
+        splits = decode_splits(T, spec.num_kv_heads, max_ctx, q.device,
+                               lib.pb_diff_attention_tc_max_splits(spec.num_heads, spec.num_kv_heads))
+        floats = lib.pb_diff_attention_tc_scratch_floats(T, spec.num_heads, spec.num_kv_heads, vdim, splits)
+        if floats:
             key = ("diff_attention_scratch", T, spec.num_heads, vdim, splits)
             scratch = batch.extras.get(key)
             if scratch is None:
-                floats = lib.pb_diff_attention_tc_scratch_floats(T, spec.num_heads, vdim, splits)
-                scratch = batch.extras[key] = torch.empty(max(1, floats), dtype=torch.float32, device=q.device)
+                scratch = batch.extras[key] = torch.empty(floats, dtype=torch.float32, device=q.device)
     else:
         tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, 64 // (spec.num_heads // spec.num_kv_heads), 0, None)
     check(lib.pb_diff_attention_tc_bf16(
