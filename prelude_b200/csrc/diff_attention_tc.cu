@@ -344,55 +344,56 @@ __global__ void __launch_bounds__(256) diff_attention_mma_kernel(const DiffAttnP
     }
 }
 
-// A block of two warps per (token, head), warp c on map c: lane s takes split s's maximum and sum (at most 32 splits),
-// the warp agrees on the common maximum and on each split's share, and every lane adds up its columns with the splits'
-// loads independent of one another.  Map 1 goes through shared memory to warp 0, which does the head's epilogue.
-__global__ void __launch_bounds__(64) diff_attention_merge_kernel(const DiffAttnParams p) {
+// A block of eight warps per (token, head): warps 0..3 on map 0, 4..7 on map 1.  In every warp lane s takes part s's
+// maximum and sum (at most 32 parts) and the warp agrees on the common maximum and on each part's share; warp w of a
+// map then adds up parts w, w + 4, ... over its columns, all loads issued before the first sum (one round trip to the
+// cache instead of one per part), the four warps' sums meet in shared memory, and warp 0 does the head's epilogue.
+__global__ void __launch_bounds__(256) diff_attention_merge_kernel(const DiffAttnParams p) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
-    __shared__ float other[256];
-    const int c = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float acc_s[2][4][256];
+    const int c = threadIdx.x >> 7, w = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;
     const int tok = blockIdx.x / p.n_heads, head = blockIdx.x % p.n_heads;
     if (p.token_row[tok] < 0) return;
     const int vdim = p.vdim, S = p.n_parts;
     const size_t at = ((size_t)tok * p.n_heads + head) * 2 + c;
     float ms = -INFINITY, ls = 0.f;
     if (lane < S) { ms = p.part_ml[(at * S + lane) * 2]; ls = p.part_ml[(at * S + lane) * 2 + 1]; }
+    const float* po = p.part_o + at * S * vdim;
+    float v[8][8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int part = w + 4 * u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int col = lane + 32 * i;
+            v[u][i] = (part < S && col < vdim) ? po[(size_t)part * vdim + col] : 0.f;
+        }
+    }
     const float M = pb_warp_max(ms);
     const float ws = ms == -INFINITY ? 0.f : exp2f(ms - M);
     const float L = pb_warp_sum(ws * ls);
-    const float share = L > 0.f ? ws / L : 0.f;               // of split `lane`
+    const float share = L > 0.f ? ws / L : 0.f;               // of part `lane`
     float a[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) a[i] = 0.f;
-    const float* po = p.part_o + at * S * vdim;
-    for (int s0 = 0; s0 < S; s0 += 4) {
-        float v[4][8], w[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            w[u] = __shfl_sync(0xffffffffu, share, min(s0 + u, 31));
+    for (int u = 0; u < 8; ++u) {
+        const float wgt = __shfl_sync(0xffffffffu, share, (w + 4 * u) & 31);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int col = lane + 32 * i;
-                v[u][i] = (s0 + u < S && col < vdim) ? po[(size_t)(s0 + u) * vdim + col] : 0.f;
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) a[i] = fmaf(s0 + u < S ? w[u] : 0.f, v[u][i], a[i]);
+        for (int i = 0; i < 8; ++i) a[i] = fmaf(w + 4 * u < S ? wgt : 0.f, v[u][i], a[i]);
     }
-    if (c == 1) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) other[lane + 32 * i] = a[i];
-    }
+    for (int i = 0; i < 8; ++i) acc_s[c][w][lane + 32 * i] = a[i];
     __syncthreads();
-    if (c == 1) return;
+    if (threadIdx.x >= 32) return;
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int col = lane + 32 * i;
-        a[i] = col < vdim ? a[i] - p.lambda * other[col] : 0.f;
+        const float a0 = (acc_s[0][0][col] + acc_s[0][1][col]) + (acc_s[0][2][col] + acc_s[0][3][col]);
+        const float a1 = (acc_s[1][0][col] + acc_s[1][1][col]) + (acc_s[1][2][col] + acc_s[1][3][col]);
+        a[i] = col < vdim ? a0 - p.lambda * a1 : 0.f;
         ss += a[i] * a[i];
     }
     ss = pb_warp_sum(ss);
@@ -403,9 +404,9 @@ __global__ void __launch_bounds__(64) diff_attention_merge_kernel(const DiffAttn
     for (int i = 0; i < 8; ++i) {
         const int col = lane + 32 * i;
         if (col < vdim) {
-            float v = a[i] * f;
-            if (gt) v *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col])));
-            dst[col] = __float2bfloat16_rn(v);
+            float x = a[i] * f;
+            if (gt) x *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col])));
+            dst[col] = __float2bfloat16_rn(x);
         }
     }
 }
@@ -505,7 +506,7 @@ PB_API int pb_diff_attention_tc_bf16(const void* q, long long q_stride, const vo
     if (n_parts > 1) {
         const long long items = (long long)n_tokens * n_heads;
         PB_REQUIRE(items < (1ll << 31), "diff_attention_tc: too many rows");
-        pb_launch(diff_attention_merge_kernel, dim3((unsigned)items), dim3(64), 0, stream, p);
+        pb_launch(diff_attention_merge_kernel, dim3((unsigned)items), dim3(256), 0, stream, p);
         PB_CHECK_LAUNCH("diff_attention_merge");
     }
     return 0;

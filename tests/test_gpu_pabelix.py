@@ -392,3 +392,21 @@ def test_tensor_core_attention_equals_the_plain_kernel(heads, kv, dim, vdim, pag
         err = (got - want).abs()
         assert float(err.max()) < 4e-2 * float(want.abs().max()) and float(err.mean()) < 4e-3 * float(want.abs().max()), \
             (float(err.max()), float(err.mean()), float(want.abs().max()))
+
+
+def test_command_line_generates_from_a_pabelix_folder(folders):
+    import json
+    import os
+    import subprocess
+    import sys
+    folder = folders[("Q", torch.float32)]
+    cfg, w = _cfg(folder), _weights(folder)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bin", "prelude"), "--model", folder, "--dtype", "f32", "--prompt-ids", "5,17,3,200",
+                          "--max-new-tokens", "5", "--temperature", "0", "--num-pages", "16", "--page-size", "16", "--ignore-eos"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    seq = [5, 17, 3, 200]
+    for _ in range(5):
+        seq.append(int(plain.forward(cfg, w, seq, torch.float64)[-1].argmax()))
+    assert json.loads(out.stdout.strip().splitlines()[0])["token_ids"] == seq[4:]
