@@ -68,6 +68,8 @@ struct GsParams {
     int out_f32;
     long long split_stride; // elements between the partial outputs of the splits of K (gridDim.y of them)
     int gated;              // W holds N gate rows, then N up rows; the output is silu(gate) * up, N wide
+    int act;                // gated: 0 silu(gate) * up; 1 a * sigmoid(alpha a) * (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit)
+    float limit, alpha;
     int* status;
 };
 
@@ -272,7 +274,13 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
                         gsum += red[(size_t)w * 16 * 8 * MT + m * 16 + rr];
                         usum += red[(size_t)w * 16 * 8 * MT + m * 16 + rr + 8];
                     }
-                    const float v = gsum / (1.0f + expf(-gsum)) * usum;
+                    float v;
+                    if (p.act == 1) {
+                        const float a = fminf(gsum, p.limit), b = fminf(fmaxf(usum, -p.limit), p.limit);
+                        v = a / (1.0f + expf(-p.alpha * a)) * (b + 1.0f);
+                    } else {
+                        v = gsum / (1.0f + expf(-gsum)) * usum;
+                    }
                     if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
                     else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
                 }
@@ -345,9 +353,9 @@ PB_API int pb_gemm_stream_supported(int M, int N, int K, long long ldw, long lon
 // gated: W is [2 N, K], N gate rows then N up rows, and out [M, N] = silu(x Wg^T) * (x Wu^T); no bias, no splits.
 // splits > 1 cuts K into that many equal parts (K %% (16 * splits) == 0): out is then float32
 // [splits][M][ldo-strided N] with split_stride elements between the parts, and the caller adds them.
-PB_API int pb_gemm_stream_bf16(const void* X, const void* W, const float* bias, void* out, int M, int N, int K,
-                               long long ldx, long long ldw, long long ldo, int out_f32, int splits, long long split_stride,
-                               int gated, int* status, cudaStream_t stream) {
+static int gs_run(const void* X, const void* W, const float* bias, void* out, int M, int N, int K, long long ldx, long long ldw,
+                  long long ldo, int out_f32, int splits, long long split_stride, int gated, int act, float limit, float alpha,
+                  int* status, cudaStream_t stream) {
     PB_REQUIRE(!gated || (splits == 1 && bias == nullptr), "gemm_stream: the gated form takes no bias and no cut of K");
     PB_REQUIRE(splits >= 1 && splits <= 16 && (splits == 1 || K % (16 * splits) == 0), "gemm_stream: K=%d cannot be cut into %d parts of whole 16-element steps", K, splits);
     PB_REQUIRE(splits == 1 || (out_f32 && split_stride >= (long long)(M - 1) * ldo + N), "gemm_stream: partial sums are float32, %d apart at least", M * N);
@@ -360,6 +368,7 @@ PB_API int pb_gemm_stream_bf16(const void* X, const void* W, const float* bias, 
     p.ldw = ldw; p.ldx = ldx; p.ldo = ldo; p.M = M; p.N = N; p.K = k_part; p.out_f32 = out_f32; p.status = status;
     p.split_stride = split_stride;
     p.gated = gated ? 1 : 0;
+    p.act = act; p.limit = limit; p.alpha = alpha;
     size_t smem;
     gs_plan(M, k_part, &p.ks, &p.n_chunks, &p.stages, &smem);
     int blocks = gs_sms() / splits;
@@ -376,4 +385,19 @@ PB_API int pb_gemm_stream_bf16(const void* X, const void* W, const float* bias, 
     else pb_launch(gemm_stream_kernel<2>, dim3(blocks, splits), dim3(GS_THREADS), smem, stream, p);
     PB_CHECK_LAUNCH("gemm_stream");
     return 0;
+}
+
+PB_API int pb_gemm_stream_bf16(const void* X, const void* W, const float* bias, void* out, int M, int N, int K,
+                               long long ldx, long long ldw, long long ldo, int out_f32, int splits, long long split_stride,
+                               int gated, int* status, cudaStream_t stream) {
+    return gs_run(X, W, bias, out, M, N, K, ldx, ldw, ldo, out_f32, splits, split_stride, gated, 0, 0.f, 0.f, status, stream);
+}
+
+// The gated form with the clamped unit in its epilogue: out [M, N] = a * sigmoid(alpha a) * (b + 1) with
+// a = min(x Wg^T, limit) and b = clamp(x Wu^T, -limit, limit); W is [2 N, K], N gate rows then N up rows.
+PB_API int pb_gemm_stream_clamped_glu_bf16(const void* X, const void* W, void* out, int M, int N, int K, long long ldx,
+                                           long long ldw, long long ldo, int out_f32, float limit, float alpha, int* status,
+                                           cudaStream_t stream) {
+    PB_REQUIRE(limit > 0.f, "gemm_stream: the clamped unit needs a positive limit");
+    return gs_run(X, W, nullptr, out, M, N, K, ldx, ldw, ldo, out_f32, 1, 0, 1, 1, limit, alpha, status, stream);
 }

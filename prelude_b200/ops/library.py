@@ -58,6 +58,8 @@ _SIGNATURES = {
     "pb_gemm_stream_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, L, I, P, P], I),
     "pb_scatter_i32": ([P, L, P, P, I, P, P], I),
     "pb_decode_advance": ([P, P, P, P, P, I, I, P], I),
+    "pb_gemm_stream_clamped_glu_bf16": ([P, P, P, I, I, I, L, L, L, I, F, F, P, P], I),
+    "pb_gemm_pair_clamped_glu_bf16": ([P, P, P, I, I, I, L, L, L, F, F, I, P, P], I),
     "pb_embed_sinusoid": ([P, P, P, I, P, P, I, I, I, P], I),
     "pb_clamped_glu": ([P, P, I, I, I, F, F, P], I),
     "pb_normed_add_rmsnorm": ([P, P, F, P, P, I, I, P, P, I, I, F, P], I),

@@ -14,7 +14,7 @@ import torch
 
 from ..config.spec import ClampedGluSpec, GatedMlpSpec
 from ..ops import kernels as K
-from ..ops.linear import gated_linear_silu, linear
+from ..ops.linear import gated_linear_clamped, gated_linear_silu, linear
 from ..weights.loader import TensorReq
 from .registry import RunContext, register_part
 
@@ -62,7 +62,9 @@ class GatedMlp:
 @register_part("feed_forward", "clamped_glu")
 class ClampedGlu:
     """down(a * sigmoid(alpha a) * (b + 1)) with a = min(gate(x), limit) and b = clamp(up(x), -limit, limit): gate and up
-    rows one below the other, one product, the activation kernel, the down projection."""
+    rows one below the other and one product with the unit in its epilogue where a kernel of this library takes the
+    shape (a decode step: the streaming kernel; a long prompt step: the paired-block tcgen05 kernel), else the
+    library product and the activation kernel; then the down projection."""
 
     def __init__(self, spec: ClampedGluSpec, prefix: str):
         self.spec, self.prefix = spec, prefix
@@ -89,5 +91,7 @@ class ClampedGlu:
         return 3 * self.spec.intermediate_size * elem + 4 * self.spec.hidden_size * 4
 
     def forward(self, x: torch.Tensor):
-        act = K.clamped_glu(linear(x, self.w_gate_up), self.spec.limit, self.spec.alpha)
+        act = gated_linear_clamped(x, self.w_gate_up, self.spec.limit, self.spec.alpha)
+        if act is None:
+            act = K.clamped_glu(linear(x, self.w_gate_up), self.spec.limit, self.spec.alpha)
         return linear(act, self.w_down, partial_sums_ok=True)

@@ -119,6 +119,24 @@ def test_clamped_gated_unit(dtype):
     assert float((got - want).abs().max()) < (1e-6 if dtype == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("rows,width,inter", [(1, 64, 48), (7, 128, 256), (100, 64, 48), (900, 256, 384), (5, 40, 56)])
+def test_clamped_unit_feed_forward_on_every_product_kernel(rows, width, inter):
+    """Few rows: the streaming product with the unit in its epilogue; hundreds: the paired-block product with it; between
+    them, and for widths that neither takes: the library product and the activation kernel.  All against the plain one."""
+    from prelude_b200.config.spec import ClampedGluSpec
+    from prelude_b200.parts.registry import RunContext, make_part
+    g = torch.Generator().manual_seed(rows + inter)
+    w = {"gate": (torch.randn(inter, width, generator=g) * 0.3).bfloat16(), "up": (torch.randn(inter, width, generator=g) * 0.3).bfloat16(),
+         "down": (torch.randn(width, inter, generator=g) * 0.1).bfloat16()}
+    x = torch.randn(rows, width, generator=g).bfloat16()
+    want = plain.clamped_glu(x.double(), {k: v.double() for k, v in w.items()}, 0.7)
+    part = make_part("feed_forward", ClampedGluSpec(width, inter, 0.7), "ff")
+    part.load(lambda name: w[name[len("ff."):]], RunContext(torch.device(DEV), torch.bfloat16))
+    got = part.forward(x.to(DEV))
+    got = got.materialize(torch.bfloat16) if hasattr(got, "materialize") else got
+    assert float((got.cpu().double() - want).abs().max()) < 2e-2 * float(want.abs().max())
+
+
 @pytest.mark.parametrize("experts,top,groups,keep", [(12, 3, 3, 2), (8, 1, 1, 1), (6, 2, 6, 3), (16, 4, 2, 1), (5, 5, 1, 1), (64, 6, 8, 3)])
 def test_router_choice_equals_the_plain_one(experts, top, groups, keep):
     from prelude_b200.ops import kernels as K
@@ -345,7 +363,7 @@ def test_trace_replay_of_a_pabelix_folder(folders, tmp_path):
 
 # -- the tensor-core attention kernel against the plain kernel -----------------------------------------------------------
 @pytest.mark.parametrize("heads,kv,dim,vdim,page,window", [(8, 2, 64, 128, 16, None), (4, 4, 48, 80, 16, None), (16, 2, 128, 64, 32, None),
-                                                        (6, 2, 32, 32, 8, 100), (2, 1, 256, 256, 64, None), (4, 1, 16, 240, 16, 33)])
+                                                        (6, 2, 32, 32, 8, 100), (2, 1, 256, 256, 64, None), (4, 1, 16, 240, 16, 33), (32, 1, 32, 64, 16, None)])
 def test_tensor_core_attention_equals_the_plain_kernel(heads, kv, dim, vdim, page, window):
     """Random keys and values in scattered pages; requests of unequal length: long portions, a portion of two tokens,
     single tokens far into a long context (their keys cut into ranges), with and without a window; then a step of
