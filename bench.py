@@ -415,10 +415,21 @@ def pabelix_kernels(pk, size):
         ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).to(torch.int32)
         w1 = (torch.randn(E, 2 * eff, width, device=dev) * 0.02).to(bf)
         w2 = (torch.randn(E, width, eff, device=dev) * 0.02).to(bf)
-        plan = K.moe_sort(ids, E)
-        h = K.moe_gemm(x, w1, plan, gated=True, gather_div=top)
-        ms1 = _event_ms(lambda: K.moe_gemm(x, w1, plan, gated=True, gather_div=top), flush=flush)
-        ms2 = _event_ms(lambda: K.moe_gemm(h, w2, plan, gated=False, out_dtype=torch.float32), flush=flush)
+        from prelude_b200.ops import linear as L
+        st = L.tc_status(dev)
+        if rows * top >= 192 * E:
+            # as the part runs a long prompt step: rows sorted by expert, both products on the paired-block tcgen05 kernel
+            plan = K.moe_sort(ids, E, 256)
+            h = K.moe_gemm_pair(K.moe_gather_rows(x, plan, top), w1, plan, True, st)
+            ms1 = _event_ms(lambda: K.moe_gemm_pair(K.moe_gather_rows(x, plan, top), w1, plan, True, st), flush=flush)
+            ms2 = _event_ms(lambda: K.moe_gemm_pair(h, w2, plan, False, st), flush=flush)
+        else:
+            plan = K.moe_sort(ids, E)
+            h = K.moe_gemm(x, w1, plan, gated=True, gather_div=top)
+            ms1 = _event_ms(lambda: K.moe_gemm(x, w1, plan, gated=True, gather_div=top), flush=flush)
+            ms2 = _event_ms(lambda: K.moe_gemm(h, w2, plan, gated=False, out_dtype=torch.float32), flush=flush)
+        if int(st.item()) != 0:
+            raise RuntimeError("a routed product raised the status word")
         flops = 2 * rows * top * 3 * eff * width
         d1 = (torch.randn(2 * top * eff, width, device=dev) * 0.02).to(bf)
         d2 = (torch.randn(width, top * eff, device=dev) * 0.02).to(bf)

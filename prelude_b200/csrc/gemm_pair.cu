@@ -81,7 +81,25 @@ struct GpParams {
     int act;                        // gated 1: 0 silu(gate) * up; 1 the clamped unit a * sigmoid(alpha a) * (b + 1)
     float limit, alpha;             //   with a = min(gate, limit), b = clamp(up, -limit, limit)
     int b_is_constant;
+    // grouped form (products of routed experts over rows sorted by expert): row tile tm of the map covers the rows
+    // tile_row0[tm] .. of expert tile_expert[tm] (negative: no such tile), which end before offsets[expert + 1]; B holds
+    // the experts' matrices one below the other, expert_rows_b rows each.  Null: the plain form.
+    const int32_t* tile_expert;
+    const int32_t* tile_row0;
+    const int32_t* offsets;
+    int expert_rows_b, map_rows_b;
 };
+
+// Where row tile tm lies: false when the grouped form has no such tile.
+__device__ __forceinline__ bool gp_tile(const GpParams& p, int tm, int& row_base, int& row_limit, int& b_off) {
+    if (p.tile_expert == nullptr) { row_base = tm * 256; row_limit = p.rows_a; b_off = 0; return true; }
+    const int e = p.tile_expert[tm];
+    if (e < 0) return false;
+    row_base = p.tile_row0[tm];
+    row_limit = p.offsets[e + 1];
+    b_off = e * p.expert_rows_b;
+    return true;
+}
 
 // ---- what the paired form adds to tcgen05.cuh ----
 __device__ __forceinline__ uint32_t gp_map_to_rank(uint32_t smem_addr, uint32_t rank) {   // the same variable in another block of the cluster
@@ -302,11 +320,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             bool ok = true;
             int fill = 0;
             bool waited = false;
-            if (!p.b_is_constant) { pb_grid_dep_wait(); waited = true; }
+            if (!p.b_is_constant || p.tile_expert) { pb_grid_dep_wait(); waited = true; }   // the tile map is the kernel before's
             for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-                const int a_row = tm * 256 + rank * GP_BM;
-                const int b_row = p.gated == 1 ? (rank == 0 ? tn * GP_HALF : p.out_cols + tn * GP_HALF) : tn * GP_BN + rank * GP_HALF;
+                int row_base, row_limit, b_off;
+                if (!gp_tile(p, tm, row_base, row_limit, b_off)) continue;
+                const int a_row = row_base + rank * GP_BM;
+                const int b_row = b_off + (p.gated == 1 ? (rank == 0 ? tn * GP_HALF : p.out_cols + tn * GP_HALF) : tn * GP_BN + rank * GP_HALF);
                 for (int kb = 0; kb < p.kblocks; ++kb, ++fill) {
                     const int stage = fill % GP_STAGES;
                     ok = tc_mbar_wait(&empty_bar[stage], ((fill / GP_STAGES) & 1) ^ 1);
@@ -328,7 +348,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint32_t idesc = gp_idesc();
             int fill = 0, seg = 0;
             bool ok = true;
-            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++seg) {
+            if (p.tile_expert) pb_grid_dep_wait();
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                if (p.tile_expert && p.tile_expert[tile % p.tiles_m] < 0) continue;       // seg counts the tiles that exist
                 const int acc = seg & 1;
                 ok = __all_sync(0xffffffffu, tc_mbar_wait(&acc_empty[acc], ((seg >> 1) & 1) ^ 1));
                 if (!ok) break;
@@ -350,6 +372,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                     __syncwarp();
                 }
+                ++seg;
             }
             if (!ok && lane == 0 && p.status) atomicExch(p.status, 9);
         }
@@ -362,8 +385,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int row = quarter * 32 + lane;                // row of the block's half = tensor-memory lane
         int seg = 0;
         bool ok = true;
-        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++seg) {
+        for (int tile = pair; tile < n_tiles; tile += n_pairs) {
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            int row_base, row_limit, b_off;
+            if (!gp_tile(p, tm, row_base, row_limit, b_off)) continue;
             const int acc = seg & 1;
             if (ok) ok = tc_mbar_wait(&acc_full[acc], (seg >> 1) & 1);
             if (!ok) s_ok = 0;
@@ -371,8 +396,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!s_ok) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * GP_BN + ((uint32_t)(quarter * 32) << 16);
-            const int gi = tm * 256 + rank * GP_BM + row;
-            const bool live = gi < p.rows_a;
+            const int gi = row_base + rank * GP_BM + row;
+            const bool live = gi < row_limit;
             __nv_bfloat16* orow = p.out + (size_t)(live ? gi : 0) * p.ldo;
             if (p.gated == 2) {
                 gp_heads_epilogue(p, taddr, tn, gi, live, side);
@@ -416,6 +441,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tc_fence_before();
             __syncwarp();
             if (lane == 0) gp_arrive_cluster(gp_map_to_rank(tc_smem(&acc_empty[acc]), 0));
+            ++seg;
         }
         if (!ok && lane == 0 && p.status) atomicExch(p.status, 10);
     }
@@ -463,7 +489,7 @@ static int gp_launch(const void* A, const void* B, long long lda, long long ldb,
     if (tiles < pairs) pairs = tiles;
     CUtensorMap ma, mb;
     if (int e = gp_make_map(&ma, A, p.rows_a, p.K, lda)) return e;
-    if (int e = gp_make_map(&mb, B, p.rows_b, p.K, ldb)) return e;
+    if (int e = gp_make_map(&mb, B, p.map_rows_b ? p.map_rows_b : p.rows_b, p.K, ldb)) return e;
     const size_t smem = (size_t)GP_STAGES * GP_STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
@@ -521,6 +547,32 @@ PB_API int pb_gemm_pair_clamped_glu_bf16(const void* A, const void* B, void* out
     p.out_cols = rows_b / 2;
     p.tiles_m = (rows_a + 255) / 256;
     p.tiles_n = (p.out_cols + GP_HALF - 1) / GP_HALF;
+    p.kblocks = (K + GP_BK - 1) / GP_BK;
+    return gp_launch(A, B, lda, ldb, p, max_pairs, stream);
+}
+
+// The grouped form: the products of routed experts.  A [places, K] holds the rows sorted by expert; B [n_experts *
+// expert_rows_b, K] the experts' matrices one below the other; the device-side map (tile_expert, tile_row0 over
+// max_m_tiles row tiles of 256, offsets) says which rows are whose.  out [places, N] bfloat16 with N = expert_rows_b,
+// or, gated, N = expert_rows_b / 2 and silu(gate sums) * up sums (an expert's matrix: N gate rows, then N up rows).
+PB_API int pb_gemm_pair_grouped_bf16(const void* A, const void* B, void* out, int places, int expert_rows_b, int n_experts, int K,
+                                     long long lda, long long ldb, long long ldo, int gated, const int32_t* tile_expert,
+                                     const int32_t* tile_row0, const int32_t* offsets, int max_m_tiles, int max_pairs,
+                                     int* status, cudaStream_t stream) {
+    PB_REQUIRE(n_experts > 0 && max_m_tiles >= 0 && pb_gemm_pair_supported(places, expert_rows_b, K, lda, ldb, gated),
+               "gemm_pair (grouped): places=%d rows per expert=%d K=%d lda=%lld ldb=%lld not taken", places, expert_rows_b, K, lda, ldb);
+    PB_REQUIRE((long long)n_experts * expert_rows_b < (1ll << 31), "gemm_pair (grouped): too many rows of B");
+    PB_REQUIRE(A && B && out && tile_expert && tile_row0 && offsets && pb_aligned(A, 16) && pb_aligned(B, 16), "gemm_pair (grouped): null or unaligned pointer");
+    if (max_m_tiles == 0) return 0;
+    if (int e = get_encode()) return e;
+    GpParams p{};
+    p.out = (__nv_bfloat16*)out; p.bias = nullptr; p.status = status; p.ldo = ldo;
+    p.rows_a = places; p.rows_b = expert_rows_b; p.K = K; p.gated = gated ? 1 : 0; p.b_is_constant = 1;
+    p.tile_expert = tile_expert; p.tile_row0 = tile_row0; p.offsets = offsets;
+    p.expert_rows_b = expert_rows_b; p.map_rows_b = n_experts * expert_rows_b;
+    p.out_cols = gated ? expert_rows_b / 2 : expert_rows_b;
+    p.tiles_m = max_m_tiles;
+    p.tiles_n = gated ? (p.out_cols + GP_HALF - 1) / GP_HALF : (p.out_cols + GP_BN - 1) / GP_BN;
     p.kblocks = (K + GP_BK - 1) / GP_BK;
     return gp_launch(A, B, lda, ldb, p, max_pairs, stream);
 }

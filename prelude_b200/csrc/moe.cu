@@ -166,7 +166,7 @@ PB_API int pb_moe_tile_rows(int n_slots, int n_experts) { return n_slots >= 48 *
 PB_API int pb_moe_sort(const int32_t* ids, int n_slots, int n_experts, int32_t* offsets, int32_t* order, int32_t* place_of,
                        int32_t* tile_expert, int32_t* tile_row0, int max_tiles, int tile_rows, cudaStream_t stream) {
     PB_REQUIRE(n_slots >= 0 && n_experts > 0 && n_experts <= MOE_MAX_EXPERTS, "moe_sort: bad sizes slots=%d E=%d", n_slots, n_experts);
-    PB_REQUIRE(tile_rows == MOE_BM || tile_rows == MOE_BM_LARGE, "moe_sort: tiles have %d or %d rows", MOE_BM, MOE_BM_LARGE);
+    PB_REQUIRE(tile_rows == MOE_BM || tile_rows == MOE_BM_LARGE || tile_rows == 256, "moe_sort: tiles have %d, %d or 256 rows", MOE_BM, MOE_BM_LARGE);
     PB_REQUIRE(max_tiles >= (n_slots + tile_rows - 1) / tile_rows + n_experts, "moe_sort: room for %d tiles is too little", max_tiles);
     PB_REQUIRE(ids && offsets && order && place_of && tile_expert && tile_row0, "moe_sort: null pointer");
     pb_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, ids, n_slots, n_experts, offsets, order, place_of, tile_expert,
@@ -535,27 +535,64 @@ PB_API int pb_moe_gemm(const void* A, long long lda, const int32_t* order, int a
     return 0;
 }
 
-// out[t, :] = sum_c w[t, c] * y[place_of[t * top + c], :], choices in ascending order, float32 sums.
+// out[place, :] = x[order[place] / div, :]: the rows of a step's tokens in the order of their places (what a product
+// that reads its rows through tensor-map copies needs).
 template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ place_of,
+__global__ void moe_gather_rows_kernel(const T* __restrict__ x, long long ldx, const int32_t* __restrict__ order, int div,
+                                       T* __restrict__ out, int width) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const size_t place = blockIdx.x;
+    const T* src = x + (size_t)(order[place] / div) * ldx;
+    T* dst = out + place * width;
+    if (width % (16 / sizeof(T)) == 0 && ldx % (16 / sizeof(T)) == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+        const int n = width / (16 / (int)sizeof(T));
+        for (int i = threadIdx.x; i < n; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+PB_API int pb_moe_gather_rows(const void* x, long long ldx, const int32_t* order, int div, void* out, int dtype, int places,
+                              int width, cudaStream_t stream) {
+    PB_REQUIRE(places >= 0 && width > 0 && div > 0 && ldx >= width, "moe_gather_rows: bad sizes");
+    PB_REQUIRE(x && order && out, "moe_gather_rows: null pointer");
+    if (places == 0) return 0;
+    PB_DISPATCH_DTYPE(dtype, T,
+        (pb_launch(moe_gather_rows_kernel<T>, dim3(places), dim3(128), 0, stream, (const T*)x, ldx, order, div, (T*)out, width)));
+    PB_CHECK_LAUNCH("moe_gather_rows");
+    return 0;
+}
+
+// out[t, :] = sum_c w[t, c] * y[place_of[t * top + c], :], choices in ascending order, float32 sums.
+template <typename T, typename TY>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const int32_t* __restrict__ place_of,
                                    const float* __restrict__ weights, T* __restrict__ out, int top, int width) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     const size_t t = blockIdx.x;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = 0.f;
-        for (int c = 0; c < top; ++c) v = fmaf(weights[t * top + c], y[(size_t)place_of[t * top + c] * width + i], v);
+        for (int c = 0; c < top; ++c) v = fmaf(weights[t * top + c], pb_ld(y + (size_t)place_of[t * top + c] * width + i), v);
         pb_st(out + t * width + i, v);
     }
 }
 
-PB_API int pb_moe_combine(const float* y, const int32_t* place_of, const float* weights, void* out, int dtype, int n_tokens,
+// y float32 (y_dtype PB_F32) or of the output's type.
+PB_API int pb_moe_combine(const void* y, int y_dtype, const int32_t* place_of, const float* weights, void* out, int dtype, int n_tokens,
                           int top, int width, cudaStream_t stream) {
+    PB_REQUIRE(y_dtype == PB_F32 || y_dtype == dtype, "moe_combine: y is float32 or of the output's type");
     PB_REQUIRE(n_tokens >= 0 && top > 0 && width > 0, "moe_combine: bad sizes");
     PB_REQUIRE(y && place_of && weights && out, "moe_combine: null pointer");
     if (n_tokens == 0) return 0;
-    PB_DISPATCH_DTYPE(dtype, T,
-        (pb_launch(moe_combine_kernel<T>, dim3(n_tokens), dim3(width >= 1024 ? 256 : 128), 0, stream, y, place_of, weights, (T*)out, top, width)));
+    if (y_dtype == PB_F32) {
+        PB_DISPATCH_DTYPE(dtype, T,
+            (pb_launch(moe_combine_kernel<T, float>, dim3(n_tokens), dim3(width >= 1024 ? 256 : 128), 0, stream, (const float*)y, place_of, weights, (T*)out, top, width)));
+    } else {
+        PB_DISPATCH_DTYPE(dtype, T,
+            (pb_launch(moe_combine_kernel<T, T>, dim3(n_tokens), dim3(width >= 1024 ? 256 : 128), 0, stream, (const T*)y, place_of, weights, (T*)out, top, width)));
+    }
     PB_CHECK_LAUNCH("moe_combine");
     return 0;
 }

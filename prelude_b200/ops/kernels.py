@@ -535,12 +535,42 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gated: bool, gathe
     return out
 
 
+def moe_gather_rows(x: torch.Tensor, plan: MoePlan, div: int) -> torch.Tensor:
+    """The rows of x in the order of the plan's places: out[place] = x[order[place] // div]."""
+    _cols(x, "x")
+    places = plan.order.numel()
+    out = torch.empty((places, x.shape[1]), dtype=x.dtype, device=x.device)
+    check(_l.library().pb_moe_gather_rows(x.data_ptr(), x.stride(0), plan.order.data_ptr(), int(div), out.data_ptr(),
+                                          dtype_code(x.dtype), places, x.shape[1], _stream()), "moe_gather_rows")
+    return out
+
+
+def moe_gemm_pair(a_sorted: torch.Tensor, w: torch.Tensor, plan: MoePlan, gated: bool, status: torch.Tensor,
+                  max_pairs: int = 0) -> torch.Tensor:
+    """The experts' products on the paired-block tcgen05 kernel: a_sorted [places, K] bfloat16 holds the rows in the
+    order of their places (``moe_gather_rows``), the plan has row tiles of 256; w as for ``moe_gemm``.  bfloat16 out."""
+    _need(a_sorted, "a_sorted", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    E, rows_w, Kdim = w.shape
+    if plan.tile_rows != 256 or a_sorted.shape != (plan.order.numel(), Kdim) or (gated and rows_w % 2):
+        raise KernelLibraryError("moe_gemm_pair: a plan of 256-row tiles and rows sorted by place are needed")
+    N = rows_w // 2 if gated else rows_w
+    out = torch.empty((a_sorted.shape[0], N), dtype=torch.bfloat16, device=a_sorted.device)
+    check(_l.library().pb_gemm_pair_grouped_bf16(
+        a_sorted.data_ptr(), w.data_ptr(), out.data_ptr(), a_sorted.shape[0], rows_w, E, Kdim, a_sorted.stride(0), Kdim,
+        out.stride(0), 1 if gated else 0, plan.tile_expert.data_ptr(), plan.tile_row0.data_ptr(), plan.offsets.data_ptr(),
+        plan.max_tiles, max_pairs, status.data_ptr(), _stream()), "gemm_pair (grouped)")
+    return out
+
+
 def moe_combine(y: torch.Tensor, plan: MoePlan, weights: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """out[t] = sum_c weights[t, c] * y[place of slot (t, c)], float32 sums; y float32 [places, width]."""
-    _need(y, "y", torch.float32)
+    """out[t] = sum_c weights[t, c] * y[place of slot (t, c)], float32 sums; y [places, width] float32 or of out_dtype."""
+    _need(y, "y")
+    if y.dtype not in (torch.float32, out_dtype):
+        raise KernelLibraryError("moe_combine: y is float32 or of the output's type")
     _need(weights, "weights", torch.float32)
     T, top = weights.shape
     out = torch.empty((T, y.shape[1]), dtype=out_dtype, device=y.device)
-    check(_l.library().pb_moe_combine(y.data_ptr(), plan.place_of.data_ptr(), weights.data_ptr(), out.data_ptr(),
+    check(_l.library().pb_moe_combine(y.data_ptr(), dtype_code(y.dtype), plan.place_of.data_ptr(), weights.data_ptr(), out.data_ptr(),
                                       dtype_code(out_dtype), T, top, y.shape[1], _stream()), "moe_combine")
     return out

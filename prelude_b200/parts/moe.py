@@ -16,14 +16,20 @@ of whose shapes depends on what the router chose, so the part can be recorded.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict
 
 import torch
 
 from ..config.spec import RoutedExpertsSpec
 from ..ops import kernels as K
+from ..ops import linear as L
 from ..weights.loader import TensorReq
 from .registry import RunContext, register_part
+
+
+# average rows per expert from which a step's products run on the paired-block tcgen05 kernel
+MOE_PAIR_MIN_ROWS = int(os.environ.get("PRELUDE_MOE_PAIR_MIN_ROWS", "192"))
 
 
 @register_part("feed_forward", "routed_experts")
@@ -64,6 +70,13 @@ class RoutedExperts:
         s = self.spec
         return s.top_k * (s.expert_size * elem + s.hidden_size * 4) + s.n_experts * 4 + s.hidden_size * elem
 
+    def pair_takes(self, x: torch.Tensor) -> bool:
+        """Whether a step's products run on the paired-block kernel: bfloat16, aligned sizes, and rows enough that an
+        expert's 256-row tiles are mostly full (PRELUDE_MOE_PAIR_MIN_ROWS rows per expert on average, default 192)."""
+        s = self.spec
+        return (x.dtype == torch.bfloat16 and L.PREFILL_GEMM != "cublas" and s.hidden_size % 8 == 0 and s.expert_size % 8 == 0
+                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.shape[0] * s.top_k >= MOE_PAIR_MIN_ROWS * s.n_experts)
+
     def route(self, x: torch.Tensor):
         """(experts int32 [T, top_k], weights float32 [T, top_k]) for the rows of x."""
         s = self.spec
@@ -73,6 +86,12 @@ class RoutedExperts:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         s = self.spec
         ids, weights = self.route(x)
+        if self.pair_takes(x):
+            # a long prompt step: rows sorted by expert, both products on the paired-block tcgen05 kernel (tiles of 256 rows)
+            plan = K.moe_sort(ids, s.n_experts, 256)
+            status = L.tc_status(x.device)
+            h = K.moe_gemm_pair(K.moe_gather_rows(x, plan, s.top_k), self.w_gate_up, plan, True, status)
+            return K.moe_combine(K.moe_gemm_pair(h, self.w_down, plan, False, status), plan, weights, x.dtype)
         # tiles of 128 rows where the experts have many rows each and the tensor-core kernel takes the shapes, else of 64
         small = x.dtype != torch.bfloat16 or s.hidden_size % 8 or s.expert_size % 8
         plan = K.moe_sort(ids, s.n_experts, 64 if small else None)

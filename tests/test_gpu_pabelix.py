@@ -158,7 +158,8 @@ def test_router_choice_equals_the_plain_one(experts, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("tokens,width,ff,experts,top", [(1, 40, 24, 6, 2), (150, 72, 10, 5, 1), (333, 64, 64, 8, 3), (70, 128, 40, 4, 4)])
+@pytest.mark.parametrize("tokens,width,ff,experts,top", [(1, 40, 24, 6, 2), (150, 72, 10, 5, 1), (333, 64, 64, 8, 3), (70, 128, 40, 4, 4),
+                                                         (1200, 64, 64, 4, 2), (700, 128, 40, 3, 1), (2100, 256, 320, 6, 3)])
 def test_routed_experts_equal_the_plain_mixture(dtype, tokens, width, ff, experts, top):
     from prelude_b200.config.spec import RoutedExpertsSpec
     from prelude_b200.parts.registry import RunContext, make_part
@@ -175,6 +176,8 @@ def test_routed_experts_equal_the_plain_mixture(dtype, tokens, width, ff, expert
     part = make_part("feed_forward", RoutedExpertsSpec(width, ff, experts, top), "ff")
     part.load(lambda name: w[name[len("ff."):]], RunContext(torch.device(DEV), dtype))
     got = part.forward(x.to(DEV)).cpu().double()
+    # many rows per expert in bfloat16: the paired-block tcgen05 product; fewer: the 128-row or the 64-row tiles
+    assert part.pair_takes(x.to(DEV)) == (dtype == torch.bfloat16 and tokens * top >= 192 * experts)
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert float((got - want).abs().max()) < tol * float(want.abs().max())
     # a token's result does not depend on who else is in the step
