@@ -29,34 +29,97 @@
 #define MOE_MAX_GTOP 8
 #define MOE_MAX_EXPERTS 1024
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int groups, int keep,
-                                 int gtop, int renorm, int32_t* __restrict__ ids, float* __restrict__ weights) {
+// Router logits in 32-bit: out[t, e] = sum_k x[t, k] * W[e, k], every product exact in float32 (the operands are
+// float32, or bfloat16 whose products fit), float32 sums.  A warp takes a token and four experts; a lane sums every
+// 32nd element in ascending order and the lanes meet in a fixed tree, so the order depends on K alone.
+template <typename T>
+__global__ void __launch_bounds__(128) router_logits_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ W,
+                                                            float* __restrict__ out, int n_tokens, int n_experts, int K) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int per_token = (n_experts + 3) / 4;
+    const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= (long long)n_tokens * per_token) return;
+    const int t = (int)(item / per_token), e0 = (int)(item % per_token) * 4;
+    const T* xr = x + (size_t)t * ldx;
+    const T* w0 = W + (size_t)e0 * K;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int k = lane; k < K; k += 32) {
+        const float xv = pb_ld(xr + k);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (e0 + j < n_experts) acc[j] = fmaf(xv, pb_ld(w0 + (size_t)j * K + k), acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float v = pb_warp_sum(acc[j]);
+        if (lane == 0 && e0 + j < n_experts) out[(size_t)t * n_experts + e0 + j] = v;
+    }
+}
+
+PB_API int pb_router_logits(const void* x, long long ldx, const void* W, float* out, int dtype, int n_tokens, int n_experts, int K,
+                            cudaStream_t stream) {
+    PB_REQUIRE(n_tokens >= 0 && n_experts > 0 && K > 0 && ldx >= K, "router_logits: bad sizes T=%d E=%d K=%d", n_tokens, n_experts, K);
+    PB_REQUIRE(x && W && out, "router_logits: null pointer");
+    if (n_tokens == 0) return 0;
+    const long long items = (long long)n_tokens * ((n_experts + 3) / 4);
+    PB_REQUIRE((items + 3) / 4 < (1ll << 31), "router_logits: too many rows");
+    PB_DISPATCH_DTYPE(dtype, T,
+        (pb_launch(router_logits_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (const T*)x, ldx, (const T*)W, out,
+                   n_tokens, n_experts, K)));
+    PB_CHECK_LAUNCH("router_logits");
+    return 0;
+}
+
+// One warp per token.  Lane l holds the scores of experts l, l + 32, ...; a choice is a warp-wide argmax (larger
+// score, then smaller index), so a token costs (groups * gtop + top) rounds of five shuffles instead of as many
+// passes of one thread over all experts.
+__device__ __forceinline__ void moe_warp_argmax(float& val, int& idx) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, val, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > val || (ov == val && oi < idx)) { val = ov; idx = oi; }
+    }
+}
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top,
+                                                        int groups, int keep, int gtop, int renorm, int32_t* __restrict__ ids,
+                                                        float* __restrict__ weights) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= n_tokens) return;
     const float* z = logits + (size_t)t * n_experts;
     const int per = n_experts / groups;
+    const int slots = (n_experts + 31) / 32;                 // experts per lane, 32 at most
+    float sc[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int e = lane + 32 * i;
+        sc[i] = (i < slots && e < n_experts) ? 1.0f / (1.0f + expf(-z[e])) : -1.0f;
+    }
     unsigned long long allowed = groups >= 64 ? ~0ull : ((1ull << groups) - 1ull);
     if (keep < groups) {
         float gscore[MOE_MAX_GROUPS];
         for (int g = 0; g < groups; ++g) {
-            // the sum of the group's gtop largest scores
-            int taken[MOE_MAX_GTOP];
+            unsigned taken = 0u;
             float sum = 0.f;
             const int n = min(gtop, per);
             for (int r = 0; r < n; ++r) {
-                int best = -1;
-                float bs = 0.f;
-                for (int i = 0; i < per; ++i) {
-                    bool used = false;
-                    for (int u = 0; u < r; ++u) used |= taken[u] == i;
-                    if (used) continue;
-                    const float s = 1.0f / (1.0f + expf(-z[g * per + i]));
-                    if (best < 0 || s > bs) { best = i; bs = s; }
+                float val = -1.0f;
+                int idx = 0x7fffffff;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int e = lane + 32 * i;
+                    if (i < slots && e < n_experts && e / per == g && !((taken >> i) & 1u) && sc[i] > val) { val = sc[i]; idx = e; }
                 }
-                taken[r] = best;
-                sum += bs;
+                moe_warp_argmax(val, idx);
+                sum += fmaxf(val, 0.f);
+                if (idx < n_experts && (idx & 31) == lane) taken |= 1u << (idx >> 5);
             }
             gscore[g] = sum;
         }
@@ -70,27 +133,30 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens,
             allowed |= 1ull << best;
         }
     }
-    int chosen[MOE_MAX_TOP];
-    float score[MOE_MAX_TOP];
-    float total = 0.f;
+    unsigned chosen = 0u;
+    int my_id = 0;
+    float my_w = 0.f, total = 0.f;
     for (int r = 0; r < top; ++r) {
-        int best = -1;
-        float bs = 0.f;
-        for (int e = 0; e < n_experts; ++e) {
-            if (!((allowed >> (e / per)) & 1ull)) continue;
-            bool used = false;
-            for (int u = 0; u < r; ++u) used |= chosen[u] == e;
-            if (used) continue;
-            const float s = 1.0f / (1.0f + expf(-z[e]));
-            if (best < 0 || s > bs) { best = e; bs = s; }
+        float val = -1.0f;
+        int idx = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int e = lane + 32 * i;
+            if (i < slots && e < n_experts && ((allowed >> (e / per)) & 1ull) && !((chosen >> i) & 1u) && sc[i] > val) { val = sc[i]; idx = e; }
         }
-        chosen[r] = best;
-        score[r] = bs;
-        total += bs;
+        moe_warp_argmax(val, idx);
+        if (idx >= n_experts) {                              // scores that are no numbers: any allowed expert not yet chosen
+            idx = 0;
+            val = 0.f;
+        } else if ((idx & 31) == lane) {
+            chosen |= 1u << (idx >> 5);
+        }
+        total += val;
+        if (lane == r) { my_id = idx; my_w = val; }
     }
-    for (int r = 0; r < top; ++r) {
-        ids[(size_t)t * top + r] = chosen[r];
-        weights[(size_t)t * top + r] = renorm ? score[r] / total : score[r];
+    if (lane < top) {
+        ids[(size_t)t * top + lane] = my_id;
+        weights[(size_t)t * top + lane] = renorm ? my_w / total : my_w;
     }
 }
 
@@ -103,7 +169,7 @@ PB_API int pb_moe_route(const float* logits, int n_tokens, int n_experts, int to
     PB_REQUIRE(top <= keep * (n_experts / groups), "moe_route: top=%d experts cannot come from %d groups of %d", top, keep, n_experts / groups);
     PB_REQUIRE(logits && ids && weights, "moe_route: null pointer");
     if (n_tokens == 0) return 0;
-    pb_launch(moe_route_kernel, dim3((n_tokens + 63) / 64), dim3(64), 0, stream, logits, n_tokens, n_experts, top, groups, keep, gtop,
+    pb_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, n_tokens, n_experts, top, groups, keep, gtop,
               renorm, ids, weights);
     PB_CHECK_LAUNCH("moe_route");
     return 0;

@@ -363,6 +363,85 @@ __global__ void normed_add_rmsnorm_kernel(const TX* __restrict__ x, const float*
     }
 }
 
+// The same for every row of the stream, four elements per thread and access, all loads of the row issued before the
+// first sum and the row kept in registers between the passes.  width % 4 == 0, width <= 4 * blockDim * ITERS.
+template <typename TX, typename TY, int ITERS>
+__global__ void normed_add_rmsnorm_vec4_kernel(const TX* __restrict__ x, const float* __restrict__ wx, float eps_x,
+                                               float* __restrict__ res, const float* __restrict__ w, TY* __restrict__ y, int width,
+                                               float eps) {
+    pb_grid_dep_launch();
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int n4 = width >> 2;
+    float4 gx[ITERS], gw[ITERS];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {                     // the scales are written by no kernel: fetched before the wait
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i < n4) {
+            gx[it] = reinterpret_cast<const float4*>(wx)[i];
+            if (w) gw[it] = reinterpret_cast<const float4*>(w)[i];
+        }
+    }
+    pb_grid_dep_wait();
+    float4 xv[ITERS], rv[ITERS];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i < n4) {
+            rv[it] = reinterpret_cast<const float4*>(res + row * width)[i];
+            const TX* xr = x + row * width + 4 * (size_t)i;
+            if constexpr (sizeof(TX) == 2) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(xr);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+                xv[it] = make_float4(a.x, a.y, b.x, b.y);
+            } else {
+                xv[it] = *reinterpret_cast<const float4*>(xr);
+            }
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i < n4) { ss += xv[it].x * xv[it].x; ss += xv[it].y * xv[it].y; ss += xv[it].z * xv[it].z; ss += xv[it].w * xv[it].w; }
+    }
+    const float inv_x = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps_x);
+    ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i < n4) {
+            float4 v = rv[it];
+            v.x += xv[it].x * inv_x * gx[it].x; v.y += xv[it].y * inv_x * gx[it].y;
+            v.z += xv[it].z * inv_x * gx[it].z; v.w += xv[it].w * inv_x * gx[it].w;
+            reinterpret_cast<float4*>(res + row * width)[i] = v;
+            rv[it] = v;
+            ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+        }
+    }
+    if (y == nullptr) return;
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i < n4) {
+            const float4 v = rv[it], g = gw[it];
+            const float o0 = v.x * inv * g.x, o1 = v.y * inv * g.y, o2 = v.z * inv * g.z, o3 = v.w * inv * g.w;
+            TY* out = y + row * width + 4 * (size_t)i;
+            if constexpr (sizeof(TY) == 2) {
+                const __nv_bfloat162 p0 = __floats2bfloat162_rn(o0, o1), p1 = __floats2bfloat162_rn(o2, o3);
+                uint2 raw;
+                raw.x = *reinterpret_cast<const uint32_t*>(&p0);
+                raw.y = *reinterpret_cast<const uint32_t*>(&p1);
+                *reinterpret_cast<uint2*>(out) = raw;
+            } else {
+                *reinterpret_cast<float4*>(out) = make_float4(o0, o1, o2, o3);
+            }
+        }
+    }
+}
+
 // x [n_rows_total, width] of type dtype; wx, w float32 [width]; res float32 [n_rows_total, width]; rows null (every
 // row, res updated) or int32 [n_out] (those rows, res untouched); y [n_out, width] of type dtype, or null with w.
 PB_API int pb_normed_add_rmsnorm(const void* x, const float* wx, float eps_x, float* res, const int32_t* rows, int n_out,
@@ -372,6 +451,21 @@ PB_API int pb_normed_add_rmsnorm(const void* x, const float* wx, float eps_x, fl
     PB_REQUIRE(x && wx && res && ((w == nullptr) == (y == nullptr)), "normed_add_rmsnorm: null pointer");
     PB_REQUIRE(rows == nullptr ? n_out == n_rows_total : y != nullptr, "normed_add_rmsnorm: rows and outputs do not fit");
     if (n_out == 0) return 0;
+    const int threads = norm_threads(width);
+    const size_t esz = dtype == PB_BF16 ? 2 : 4;
+    if (rows == nullptr && width % 4 == 0 && width <= 4 * threads * 8 && pb_aligned(x, 4 * esz) && pb_aligned(wx, 16) && pb_aligned(res, 16) &&
+        (w == nullptr || (pb_aligned(w, 16) && pb_aligned(y, 4 * esz)))) {
+        const int iters = (width / 4 + threads - 1) / threads;
+#define NA_VEC(IT)                                                                                                              \
+    PB_DISPATCH_DTYPE(dtype, T, (pb_launch(normed_add_rmsnorm_vec4_kernel<T, T, IT>, dim3(n_out), dim3(threads), 0, stream, (const T*)x, wx, \
+                                           eps_x, res, w, (T*)y, width, eps)))
+        if (iters <= 2) NA_VEC(2);
+        else if (iters <= 4) NA_VEC(4);
+        else NA_VEC(8);
+#undef NA_VEC
+        PB_CHECK_LAUNCH("normed_add_rmsnorm");
+        return 0;
+    }
     const int keep = (size_t)width * sizeof(float) <= 40 * 1024 ? 1 : 0;
     const size_t smem = keep ? (size_t)width * sizeof(float) : 0;
     PB_DISPATCH_DTYPE(dtype, T,

@@ -476,6 +476,19 @@ def diff_attention_ref(q: torch.Tensor, gate: Optional[torch.Tensor], k_pages: t
     return out
 
 
+def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [T, K] times w [E, K] transposed as float32 [T, E]: exact products, float32 sums in an order that depends on K alone."""
+    _cols(x, "x")
+    _need(w, "w", x.dtype)
+    T, Kdim = x.shape
+    if w.dim() != 2 or w.shape[1] != Kdim:
+        raise KernelLibraryError(f"router_logits: x {tuple(x.shape)} against w {tuple(w.shape)}")
+    out = torch.empty((T, w.shape[0]), dtype=torch.float32, device=x.device)
+    check(_l.library().pb_router_logits(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), dtype_code(x.dtype), T, w.shape[0],
+                                        Kdim, _stream()), "router_logits")
+    return out
+
+
 def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, group_top: int, renormalize: bool):
     """float32 router logits [T, E] -> (experts int32 [T, top], weights float32 [T, top])."""
     _need(logits, "logits", torch.float32)

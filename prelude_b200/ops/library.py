@@ -69,6 +69,7 @@ _SIGNATURES = {
     "pb_diff_attention_tc_scratch_floats": ([I, I, I, I, I], L),
     "pb_diff_attention_tc_max_splits": ([I, I], I),
     "pb_diff_attention_tc_bf16": ([P, L, P, L, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, I, F, F, F, I, I, I, I, I, P, P, P], I),
+    "pb_router_logits": ([P, L, P, P, I, I, I, I, P], I),
     "pb_moe_route": ([P, I, I, I, I, I, I, I, P, P, P], I),
     "pb_moe_tile_rows": ([I, I], I),
     "pb_moe_sort": ([P, I, I, P, P, P, P, P, I, I, P], I),

@@ -2,7 +2,7 @@
 
 The router's logits are a 32-bit product of the feed-forward's input with the
 router matrix (float32 sums of exact products on the float32 units, whatever
-the run's type).  Scores are their sigmoids; experts form equal groups of
+the run's type: ``kernels.router_logits``).  Scores are their sigmoids; experts form equal groups of
 neighbours, a group scores the sum of its largest scores, and only experts of
 the best groups can be chosen; the chosen scores weigh the experts' outputs
 (``RoutedExpertsSpec`` has the constants).
@@ -80,7 +80,7 @@ class RoutedExperts:
     def route(self, x: torch.Tensor):
         """(experts int32 [T, top_k], weights float32 [T, top_k]) for the rows of x."""
         s = self.spec
-        logits = K.gemm_ref(x, self.w_router, None, torch.float32)
+        logits = K.router_logits(x, self.w_router)
         return K.moe_route(logits, s.top_k, s.n_groups, s.keep_groups, s.group_score_top, s.renormalize)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
