@@ -424,10 +424,11 @@ def pabelix_kernels(pk, size):
             ms1 = _event_ms(lambda: K.moe_gemm_pair(K.moe_gather_rows(x, plan, top), w1, plan, True, st), flush=flush)
             ms2 = _event_ms(lambda: K.moe_gemm_pair(h, w2, plan, False, st), flush=flush)
         else:
-            plan = K.moe_sort(ids, E)
-            h = K.moe_gemm(x, w1, plan, gated=True, gather_div=top)
-            ms1 = _event_ms(lambda: K.moe_gemm(x, w1, plan, gated=True, gather_div=top), flush=flush)
-            ms2 = _event_ms(lambda: K.moe_gemm(h, w2, plan, gated=False, out_dtype=torch.float32), flush=flush)
+            few = rows * top <= 6 * E                        # as the part runs a decode step: the kernel that streams the weights
+            plan = K.moe_sort(ids, E, 64 if few else None)
+            h = K.moe_gemm(x, w1, plan, gated=True, gather_div=top, few_rows=few)
+            ms1 = _event_ms(lambda: K.moe_gemm(x, w1, plan, gated=True, gather_div=top, few_rows=few), flush=flush)
+            ms2 = _event_ms(lambda: K.moe_gemm(h, w2, plan, gated=False, out_dtype=torch.float32, few_rows=few), flush=flush)
         if int(st.item()) != 0:
             raise RuntimeError("a routed product raised the status word")
         flops = 2 * rows * top * 3 * eff * width

@@ -601,6 +601,119 @@ PB_API int pb_moe_gemm(const void* A, long long lda, const int32_t* order, int a
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The products of a decode step, where an expert has a row or a few: nothing but the experts' weights to stream.  A
+// warp owns two output features (gated: their two gate rows and two up rows), reads those weight rows once in 16-byte
+// pieces, 256 elements of K per step, and multiplies them with up to four rows of the tile at a time, which come from
+// the first-level cache; float32 sums, lanes met in a fixed tree.  Tiles are the 64-row tiles of the map; an expert
+// with more than four rows walks its weights again for the next four.  Needs K % 8 == 0 and 16-byte aligned rows.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void moe_unpack8(const uint4& raw, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(h[i]);
+        f[2 * i] = v.x;
+        f[2 * i + 1] = v.y;
+    }
+}
+
+template <typename TC, bool GATED>
+__global__ void __launch_bounds__(256) moe_gemv_kernel(const __nv_bfloat16* __restrict__ A, long long lda,
+                                                       const int32_t* __restrict__ order, int a_div,
+                                                       const __nv_bfloat16* __restrict__ W, long long w_expert_stride, int N, int K,
+                                                       const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ tile_row0,
+                                                       const int32_t* __restrict__ offsets, TC* __restrict__ C, long long ldc) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int row0 = tile_row0[blockIdx.x];
+    const int rows = min(MOE_BM, offsets[e + 1] - row0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f0 = (blockIdx.y * 8 + warp) * 2;
+    if (f0 >= N) return;
+    constexpr int NW = GATED ? 4 : 2;
+    const __nv_bfloat16* We = W + (size_t)e * w_expert_stride;
+    const __nv_bfloat16* wrow[NW];
+#pragma unroll
+    for (int j = 0; j < NW; ++j) {
+        const int f = min(f0 + (j & 1), N - 1);
+        wrow[j] = We + (size_t)((GATED && j >= 2 ? N : 0) + f) * K;
+    }
+    for (int r0 = 0; r0 < rows; r0 += 4) {
+        const int R = min(4, rows - r0);
+        const __nv_bfloat16* xrow[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int pl = row0 + r0 + min(r, R - 1);
+            xrow[r] = A + (size_t)(order ? order[pl] / a_div : pl) * lda;
+        }
+        float acc[NW][4];
+#pragma unroll
+        for (int j = 0; j < NW; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+#pragma unroll 2
+        for (int k = lane * 8; k < K; k += 256) {
+            uint4 wv[NW], xv[4];
+#pragma unroll
+            for (int j = 0; j < NW; ++j) wv[j] = *reinterpret_cast<const uint4*>(wrow[j] + k);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) xv[r] = *reinterpret_cast<const uint4*>(xrow[r] + k);
+            float xf[4][8];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) moe_unpack8(xv[r], xf[r]);
+#pragma unroll
+            for (int j = 0; j < NW; ++j) {
+                float wf[8];
+                moe_unpack8(wv[j], wf);
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[j][r] = fmaf(wf[i], xf[r][i], acc[j][r]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NW; ++j)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[j][r] = pb_warp_sum(acc[j][r]);
+        if (lane < 8) {                                      // lane = 2 * row + feature
+            const int r = lane >> 1, q = lane & 1;
+            if (r < R && f0 + q < N) {
+                float v = 0.f, u = 0.f;
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+                    for (int qq = 0; qq < 2; ++qq)
+                        if (rr == r && qq == q) { v = acc[qq][rr]; if (GATED) u = acc[GATED ? 2 + qq : qq][rr]; }
+                if (GATED) v = v / (1.0f + expf(-v)) * u;
+                pb_st(C + (size_t)(row0 + r0 + r) * ldc + f0 + q, v);
+            }
+        }
+    }
+}
+
+// As pb_moe_gemm for bfloat16 operands and a map of 64-row tiles, on the streaming kernel above.
+PB_API int pb_moe_gemv(const void* A, long long lda, const int32_t* order, int a_div, const void* W, long long w_expert_stride,
+                       int N, int K, int gated, const int32_t* tile_expert, const int32_t* tile_row0, const int32_t* offsets,
+                       int max_tiles, void* C, long long ldc, int out_dtype, cudaStream_t stream) {
+    PB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && w_expert_stride % 8 == 0 && max_tiles >= 0 && a_div > 0,
+               "moe_gemv: N=%d K=%d lda=%lld: K and the strides in multiples of 8", N, K, lda);
+    PB_REQUIRE(A && W && C && tile_expert && tile_row0 && offsets && pb_aligned(A, 16) && pb_aligned(W, 16), "moe_gemv: null or unaligned pointer");
+    PB_REQUIRE(lda >= K && ldc >= N && w_expert_stride >= (long long)(gated ? 2 : 1) * N * K, "moe_gemv: a stride is shorter than its row");
+    if (max_tiles == 0) return 0;
+    dim3 grid(max_tiles, (N + 15) / 16);
+    PB_REQUIRE(grid.y < 65536, "moe_gemv: N=%d too large", N);
+#define MOE_GEMV(TCC, G)                                                                                                              \
+    pb_launch(moe_gemv_kernel<TCC, G>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)A, lda, order, a_div, (const __nv_bfloat16*)W, \
+              w_expert_stride, N, K, tile_expert, tile_row0, offsets, (TCC*)C, ldc)
+    if (out_dtype == PB_F32) { if (gated) MOE_GEMV(float, true); else MOE_GEMV(float, false); }
+    else if (out_dtype == PB_BF16) { if (gated) MOE_GEMV(__nv_bfloat16, true); else MOE_GEMV(__nv_bfloat16, false); }
+    else return pb_fail("moe_gemv: unknown output type code %d", out_dtype);
+#undef MOE_GEMV
+    PB_CHECK_LAUNCH("moe_gemv");
+    return 0;
+}
+
 // out[place, :] = x[order[place] / div, :]: the rows of a step's tokens in the order of their places (what a product
 // that reads its rows through tensor-map copies needs).
 template <typename T>

@@ -526,10 +526,11 @@ def moe_sort(ids: torch.Tensor, n_experts: int, tile_rows: Optional[int] = None)
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gated: bool, gather_div: int = 0,
-             out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+             out_dtype: Optional[torch.dtype] = None, few_rows: bool = False) -> torch.Tensor:
     """The experts' products over the plan's places.  a [rows, K]; w [E, N (2 N when gated: gate rows, then up rows), K];
     row of place p is ``order[p] // gather_div`` (the token of a slot) or, with gather_div 0, p itself.  Returns
-    [places, N]: a W_e^T, or silu(a Wg_e^T) * (a Wu_e^T)."""
+    [places, N]: a W_e^T, or silu(a Wg_e^T) * (a Wu_e^T).  ``few_rows``: the experts have a row or a few each (a decode
+    step): the kernel that only streams the weights, where it takes the operands (bfloat16, K in multiples of 8)."""
     _cols(a, "a")
     _need(w, "w", a.dtype)
     E, rows_w, Kdim = w.shape
@@ -541,6 +542,13 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gated: bool, gathe
         raise KernelLibraryError("moe_gemm: a plan of 128-row tiles is for bfloat16 operands with K in multiples of 8")
     places = plan.order.numel()
     out = torch.empty((places, N), dtype=out_dtype, device=a.device)
+    if (few_rows and plan.tile_rows == 64 and a.dtype == torch.bfloat16 and Kdim % 8 == 0 and a.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        check(_l.library().pb_moe_gemv(a.data_ptr(), a.stride(0), plan.order.data_ptr() if gather_div else None, max(1, gather_div),
+                                       w.data_ptr(), w.stride(0), N, Kdim, 1 if gated else 0, plan.tile_expert.data_ptr(),
+                                       plan.tile_row0.data_ptr(), plan.offsets.data_ptr(), plan.max_tiles, out.data_ptr(), out.stride(0),
+                                       dtype_code(out_dtype), _stream()), "moe_gemv")
+        return out
     check(_l.library().pb_moe_gemm(a.data_ptr(), a.stride(0), plan.order.data_ptr() if gather_div else None, max(1, gather_div),
                                    w.data_ptr(), w.stride(0), N, Kdim, 1 if gated else 0, plan.tile_expert.data_ptr(),
                                    plan.tile_row0.data_ptr(), plan.offsets.data_ptr(), plan.max_tiles, plan.tile_rows, out.data_ptr(), out.stride(0),

@@ -74,6 +74,7 @@ _SIGNATURES = {
     "pb_moe_tile_rows": ([I, I], I),
     "pb_moe_sort": ([P, I, I, P, P, P, P, P, I, I, P], I),
     "pb_moe_gemm": ([P, L, P, I, P, L, I, I, I, P, P, P, I, I, P, L, I, I, P], I),
+    "pb_moe_gemv": ([P, L, P, I, P, L, I, I, I, P, P, P, I, P, L, I, P], I),
     "pb_moe_combine": ([P, I, P, P, P, I, I, I, I, P], I),
     "pb_moe_gather_rows": ([P, L, P, I, P, I, I, I, P], I),
     "pb_gemm_pair_grouped_bf16": ([P, P, P, I, I, I, I, L, L, L, I, P, P, P, I, I, P, P], I),

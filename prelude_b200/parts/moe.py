@@ -28,6 +28,8 @@ from ..weights.loader import TensorReq
 from .registry import RunContext, register_part
 
 
+# average rows per expert up to which a step's products run on the kernel that only streams the experts' weights
+MOE_FEW_ROWS = int(os.environ.get("PRELUDE_MOE_FEW_ROWS", "6"))
 # average rows per expert from which a step's products run on the paired-block tcgen05 kernel
 MOE_PAIR_MIN_ROWS = int(os.environ.get("PRELUDE_MOE_PAIR_MIN_ROWS", "192"))
 
@@ -94,7 +96,8 @@ class RoutedExperts:
             return K.moe_combine(K.moe_gemm_pair(h, self.w_down, plan, False, status), plan, weights, x.dtype)
         # tiles of 128 rows where the experts have many rows each and the tensor-core kernel takes the shapes, else of 64
         small = x.dtype != torch.bfloat16 or s.hidden_size % 8 or s.expert_size % 8
-        plan = K.moe_sort(ids, s.n_experts, 64 if small else None)
-        h = K.moe_gemm(x, self.w_gate_up, plan, gated=True, gather_div=s.top_k)
-        y = K.moe_gemm(h, self.w_down, plan, gated=False, out_dtype=torch.float32)
+        few = not small and x.shape[0] * s.top_k <= MOE_FEW_ROWS * s.n_experts       # a decode step: stream the weights
+        plan = K.moe_sort(ids, s.n_experts, 64 if (small or few) else None)
+        h = K.moe_gemm(x, self.w_gate_up, plan, gated=True, gather_div=s.top_k, few_rows=few)
+        y = K.moe_gemm(h, self.w_down, plan, gated=False, out_dtype=torch.float32, few_rows=few)
         return K.moe_combine(y, plan, weights, x.dtype)
