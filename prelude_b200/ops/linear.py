@@ -103,7 +103,8 @@ def gated_linear_clamped(x: torch.Tensor, weight_gate_up: torch.Tensor, limit: f
             x.data_ptr(), weight_gate_up.data_ptr(), out.data_ptr(), M, N, Kdim, x.stride(0), weight_gate_up.stride(0), N, 0,
             float(limit), float(alpha), tc_status(x.device).data_ptr(), _l.current_stream_ptr(x.device)), "gemm_stream (clamped unit)")
         return out
-    if PREFILL_GEMM != "cublas" and M >= PAIR_MIN_ROWS and pair_takes(x, weight_gate_up, gated=True):
+    # (operands no smaller than one copy box of the kernel: 128 rows of 64 elements)
+    if (PREFILL_GEMM != "cublas" and M >= PAIR_MIN_ROWS and N >= 128 and Kdim >= 64 and pair_takes(x, weight_gate_up, gated=True)):
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         check(_l.library().pb_gemm_pair_clamped_glu_bf16(
             x.data_ptr(), weight_gate_up.data_ptr(), out.data_ptr(), M, weight_gate_up.shape[0], Kdim, x.stride(0),

@@ -77,7 +77,9 @@ class RoutedExperts:
         expert's 256-row tiles are mostly full (PRELUDE_MOE_PAIR_MIN_ROWS rows per expert on average, default 192)."""
         s = self.spec
         return (x.dtype == torch.bfloat16 and L.PREFILL_GEMM != "cublas" and s.hidden_size % 8 == 0 and s.expert_size % 8 == 0
-                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.shape[0] * s.top_k >= MOE_PAIR_MIN_ROWS * s.n_experts)
+                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.shape[0] * s.top_k >= MOE_PAIR_MIN_ROWS * s.n_experts
+                # operands no smaller than one copy box of the kernel (128 rows of 64 elements)
+                and s.hidden_size >= 64 and s.expert_size >= 64 and s.n_experts * min(s.hidden_size, 2 * s.expert_size) >= 128)
 
     def route(self, x: torch.Tensor):
         """(experts int32 [T, top_k], weights float32 [T, top_k]) for the rows of x."""
