@@ -29,7 +29,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import torch
 
 from ..engine.batch import LayerCache
-from ..parts.registry import KvPagesNeed, StateNeed
+from ..parts.registry import CombinedNeed, KvPagesNeed, StateNeed, leaf_needs
 from .pages import CacheAccountingError, OutOfPages, PageAllocator, SlotAllocator
 
 
@@ -41,7 +41,7 @@ def _ceil_div(a: int, b: int) -> int:
 class KvGroup:
     gid: int
     need: KvPagesNeed
-    members: List[int]
+    members: List[object]            # order index, or (order index, path...) for a member of a combined need
     allocator: PageAllocator
     k_pages: Dict[int, torch.Tensor] = field(default_factory=dict)
     v_pages: Dict[int, torch.Tensor] = field(default_factory=dict)
@@ -75,21 +75,22 @@ class CacheManager:
         self.state_needs: Dict[int, StateNeed] = {}
         self.state_tensors: Dict[int, torch.Tensor] = {}
         by_need: Dict[KvPagesNeed, KvGroup] = {}
-        for n, need in enumerate(needs):
-            if need is None:
-                continue
-            if isinstance(need, KvPagesNeed):
-                g = by_need.get(need)
-                if g is None:
-                    g = KvGroup(len(self.groups), need, [], PageAllocator(num_pages))
-                    by_need[need] = g
-                    self.groups.append(g)
-                g.members.append(n)
-                self.group_of[n] = g.gid
-            elif isinstance(need, StateNeed):
-                self.state_needs[n] = need
-            else:
-                raise TypeError(f"order entry {n}: unknown cache need {need!r}")
+        self.needs = list(needs)
+        for n, top in enumerate(needs):
+            for path, need in leaf_needs(top):
+                key = n if not path else (n,) + path
+                if isinstance(need, KvPagesNeed):
+                    g = by_need.get(need)
+                    if g is None:
+                        g = KvGroup(len(self.groups), need, [], PageAllocator(num_pages))
+                        by_need[need] = g
+                        self.groups.append(g)
+                    g.members.append(key)
+                    self.group_of[key] = g.gid
+                elif isinstance(need, StateNeed):
+                    self.state_needs[key] = need
+                else:
+                    raise TypeError(f"order entry {n}: unknown cache need {need!r}")
         self.slots = SlotAllocator(max_slots)
         self.requests: Dict[Hashable, RequestCache] = {}
         self._fresh_slots: List[int] = []
@@ -115,19 +116,33 @@ class CacheManager:
                 g.k_pages[n] = torch.zeros(shape, dtype=self.dtype, device=self.device)
                 g.v_pages[n] = torch.zeros(v_shape, dtype=self.dtype, device=self.device)
         for n, need in self.state_needs.items():
-            self.state_tensors[n] = torch.zeros((self.max_slots,) + tuple(need.shape), dtype=need.dtype, device=self.device)
+            self.state_tensors[n] = torch.zeros((self.max_slots,) + tuple(need.shape), dtype=need.dtype or self.dtype, device=self.device)
 
     @staticmethod
     def bytes_per_page(needs: Sequence[object], page_size: int, elem_size: int) -> int:
         """Device bytes that one page id costs over all groups and layers."""
         total = 0
-        for need in needs:
-            if isinstance(need, KvPagesNeed):
-                total += page_size * need.elements_per_token * elem_size
+        for top in needs:
+            for _, need in leaf_needs(top):
+                if isinstance(need, KvPagesNeed):
+                    total += page_size * need.elements_per_token * elem_size
         return total
 
     def layer_cache(self, n: int) -> LayerCache:
         """What entry n of the run order reads and writes."""
+        top = self.needs[n] if isinstance(n, int) and n < len(self.needs) else None
+        if isinstance(top, CombinedNeed):
+            return self._combined_cache(top, (n,))
+        return self._leaf_cache(n)
+
+    def _combined_cache(self, need: CombinedNeed, key: tuple) -> LayerCache:
+        children = []
+        for i, part in enumerate(need.parts):
+            k = key + (i,)
+            children.append(self._combined_cache(part, k) if isinstance(part, CombinedNeed) else self._leaf_cache(k))
+        return LayerCache("combined", -1, children=tuple(children))
+
+    def _leaf_cache(self, n) -> LayerCache:
         if n in self.group_of:
             g = self.groups[self.group_of[n]]
             return LayerCache("kv", g.gid, g.k_pages.get(n), g.v_pages.get(n))

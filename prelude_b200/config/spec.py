@@ -97,6 +97,141 @@ class DiffAttentionSpec:
 
 
 @dataclass(frozen=True)
+class RotaryBandScaling:
+    """Rates rescaled by wavelength l = 2 pi / f: kept where l < original / high, divided by ``factor`` where
+    l > original / low, and blended linearly in original / l between the two."""
+    factor: float
+    low: float
+    high: float
+    original: float
+    kind: str = "bands"
+
+
+@dataclass(frozen=True)
+class RotaryRampScaling:
+    """Rates blended between f and f / factor along a ramp over the pair index i: with
+    turn(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(turn(fast)), 0),
+    hi = min(ceil(turn(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the rate is
+    f_i / factor * ramp_i + f_i (1 - ramp_i); cosine and sine are both multiplied by
+    ``amplitude_slope`` ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+    amplitude_slope: float = 0.1
+    kind: str = "ramp"
+
+
+@dataclass(frozen=True)
+class RotaryRatesSpec:
+    """Rotary position encoding given by its rates instead of tables: angle = position * rate_i in 32-bit inside
+    the kernel, rate_i = base^(-2i/dims) rescaled by ``scaling`` (None: as they are).  ``adjacent``: rate i turns
+    elements 2i and 2i + 1 of the rotated span; otherwise i and i + dims / 2.  No longest sequence is built in."""
+    dims: int
+    base: float
+    adjacent: bool = False
+    scaling: Optional[object] = None      # RotaryBandScaling | RotaryRampScaling | None
+    kind: str = "rotary_rates"
+
+
+@dataclass(frozen=True)
+class GqaSpec:
+    """Grouped-query softmax attention over a paged cache with the options that designs combine: keys and values
+    of different sizes, biases on q, k and v, an RMS norm over the whole of the q projection and of the k
+    projection (all heads at once, ``whole_qk_norm_eps``), a rotation of the first ``position.dims`` elements of
+    every head, a window (position i sees j with 0 <= i - j < window), and a learned sink per head whose
+    exponential joins the softmax's denominator.  The ``*_name`` fields are the tensors below the mixer's prefix;
+    a bias is ``<name><bias_suffix>``, a norm scale ``<name><norm_suffix>``."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    softmax_scale: float
+    position: object
+    qkv_bias: bool = False
+    whole_qk_norm_eps: Optional[float] = None
+    window: Optional[int] = None
+    sink: bool = False
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    o_name: str = "o"
+    sink_name: str = "sink"
+    bias_suffix: str = ".b"
+    norm_suffix: str = ".norm"
+    kind: str = "gqa"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values come from one cached latent per token.  Queries: c_q = norm(W_dq x),
+    q = W_uq c_q, per head [``head_dim`` plain | ``rot_dim`` rotated].  W_dkv x gives ``kv_rank`` + ``rot_dim``
+    rows: the first, normed, are the latent c; the rest, rotated, are a key part that all heads share.  Head h's
+    plain key is W_uk,h c and its value W_uv,h c; the score is (q_plain . k_plain + q_rot . k_rot) * scale.
+    Only c and the rotated key part are cached.  ``sink``: a learned number per head joins the denominator."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    value_dim: int
+    kv_rank: int
+    q_rank: int
+    softmax_scale: float
+    norm_eps: float
+    position: object
+    sink: bool = False
+    window: Optional[int] = None
+    dq_name: str = "dq"
+    uq_name: str = "uq"
+    dkv_name: str = "dkv"
+    uk_name: str = "uk"
+    uv_name: str = "uv"
+    o_name: str = "o"
+    sink_name: str = "sink"
+    norm_suffix: str = ".norm"
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """A selective state-space mixer with scalar decay per head.  W_in x is laid out [z | x | B | C | dt] with
+    inner = heads * head_dim, B and C of ``groups`` * ``state`` each, dt of ``heads``.  x, B and C pass a causal
+    convolution per channel over ``conv_taps`` tokens (last tap: the current token) with bias, then SiLU.
+    dt = softplus(dt + dt_bias).  Per head (its group: h // (heads / groups)) the state S [state, head_dim] moves as
+    S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T and y_t = S_t^T C_t + D x_t.  y * silu(z) is brought to unit
+    root mean square in ``norm_groups`` equal parts, scaled, and projected out.  The state and the last
+    ``conv_taps`` - 1 inputs of the convolution are carried per sequence."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    state: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    norm_eps: float
+    in_name: str = "in"
+    conv_name: str = "conv"
+    conv_bias_name: str = "conv.b"
+    dt_bias_name: str = "dt_bias"
+    a_log_name: str = "A_log"
+    d_name: str = "D"
+    norm_name: str = "norm"
+    o_name: str = "o"
+    kind: str = "state_space"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side on the same input; the result is the sum of their outputs, each times its
+    scale.  ``names[i]`` is mixer i's prefix below this mixer's."""
+    mixers: Tuple[object, ...]
+    scales: Tuple[float, ...]
+    names: Tuple[str, ...]
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
 class ClampedGluSpec:
     """down(a * sigmoid(alpha * a) * (b + 1)) with a = min(gate(x), limit), b = clamp(up(x), -limit, limit); no biases."""
     hidden_size: int
@@ -138,6 +273,9 @@ class GatedMlpSpec:
     hidden_size: int
     intermediate_size: int
     activation: str = "silu"
+    gate_name: str = "gate_proj.weight"
+    up_name: str = "up_proj.weight"
+    down_name: str = "down_proj.weight"
     kind: str = "gated_mlp"
 
 
@@ -159,7 +297,9 @@ class BlockSpec:
     ff_norm_name: str = "post_attention_layernorm"
     kind: str = "prenorm_residual"
     # kind "sandwich_residual": a norm after each sublayer as well, applied to its output before the residual add;
-    # there ``feed_forward`` (with its norms) may be None: a layer that is a mixer only
+    # there ``feed_forward`` (with its norms) may be None: a layer that is a mixer only.
+    # kind "postnorm_residual": only the norms after the sublayers (``mixer_norm`` and ``ff_norm`` are None): the
+    # sublayers read the residual stream itself
     mixer_post_norm: Optional[NormSpec] = None
     ff_post_norm: Optional[NormSpec] = None
     mixer_post_norm_name: str = "post_mixer_norm"

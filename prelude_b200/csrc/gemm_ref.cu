@@ -18,9 +18,13 @@
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256) gemm_ref_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
                                                        const float* __restrict__ bias, TC* __restrict__ C, int M,
-                                                       int N, int K, long long lda, long long ldw, long long ldc) {
+                                                       int N, int K, long long lda, long long ldw, long long ldc,
+                                                       long long batch_a, long long batch_w, long long batch_c) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
+    A += (size_t)blockIdx.z * batch_a;          // one product per z: the strides are 0 where there is one only
+    W += (size_t)blockIdx.z * batch_w;
+    C += (size_t)blockIdx.z * batch_c;
     __shared__ float As[GR_BK][GR_BM + 1];
     __shared__ float Ws[GR_BK][GR_BN + 1];
     const int tid = threadIdx.x;
@@ -72,27 +76,42 @@ __global__ void __launch_bounds__(256) gemm_ref_kernel(const TA* __restrict__ A,
     }
 }
 
-// in_dtype: type of A and W; out_dtype: type of C; bias float32 or null.
-// lda/ldw/ldc are row strides in elements.
-PB_API int pb_gemm_ref(const void* A, const void* W, const float* bias, void* C, int in_dtype, int out_dtype, int M,
-                       int N, int K, long long lda, long long ldw, long long ldc, cudaStream_t stream) {
-    PB_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_ref: bad sizes M=%d N=%d K=%d", M, N, K);
+static int gemm_ref_launch(const void* A, const void* W, const float* bias, void* C, int in_dtype, int out_dtype, int M, int N,
+                           int K, long long lda, long long ldw, long long ldc, int batch, long long batch_a,
+                           long long batch_w, long long batch_c, cudaStream_t stream) {
+    PB_REQUIRE(M >= 0 && N > 0 && K > 0 && batch >= 0, "gemm_ref: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
     PB_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_ref: a row stride is shorter than its row");
     PB_REQUIRE(A && W && C, "gemm_ref: null pointer");
-    if (M == 0) return 0;
-    dim3 grid((N + GR_BN - 1) / GR_BN, (M + GR_BM - 1) / GR_BM);
-    PB_REQUIRE(grid.y < 65536, "gemm_ref: M=%d too large", M);
+    if (M == 0 || batch == 0) return 0;
+    dim3 grid((N + GR_BN - 1) / GR_BN, (M + GR_BM - 1) / GR_BM, batch);
+    PB_REQUIRE(grid.y < 65536 && batch < 65536, "gemm_ref: M=%d or batch=%d too large", M, batch);
     if (in_dtype == PB_F32 && out_dtype == PB_F32)
         pb_launch(gemm_ref_kernel<float, float, float>, dim3(grid), dim3(256), 0, stream, (const float*)A, (const float*)W, bias,
-                                                                      (float*)C, M, N, K, lda, ldw, ldc);
+                                                                      (float*)C, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
     else if (in_dtype == PB_BF16 && out_dtype == PB_BF16)
-        pb_launch(gemm_ref_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, stream, 
-            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc);
+        pb_launch(gemm_ref_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, stream,
+            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
     else if (in_dtype == PB_BF16 && out_dtype == PB_F32)
-        pb_launch(gemm_ref_kernel<__nv_bfloat16, __nv_bfloat16, float>, dim3(grid), dim3(256), 0, stream, 
-            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, (float*)C, M, N, K, lda, ldw, ldc);
+        pb_launch(gemm_ref_kernel<__nv_bfloat16, __nv_bfloat16, float>, dim3(grid), dim3(256), 0, stream,
+            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, (float*)C, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
     else
         return pb_fail("gemm_ref: unsupported types in=%d out=%d", in_dtype, out_dtype);
     PB_CHECK_LAUNCH("gemm_ref");
     return 0;
+}
+
+// in_dtype: type of A and W; out_dtype: type of C; bias float32 or null.
+// lda/ldw/ldc are row strides in elements.
+PB_API int pb_gemm_ref(const void* A, const void* W, const float* bias, void* C, int in_dtype, int out_dtype, int M,
+                       int N, int K, long long lda, long long ldw, long long ldc, cudaStream_t stream) {
+    return gemm_ref_launch(A, W, bias, C, in_dtype, out_dtype, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, stream);
+}
+
+// ``batch`` products of the same sizes: product b reads A + b * batch_a and W + b * batch_w and writes
+// C + b * batch_c (strides in elements; the operands of different products may interleave, as the heads of a
+// [tokens, heads, size] tensor do).  No bias.
+PB_API int pb_gemm_ref_batched(const void* A, const void* W, void* C, int in_dtype, int out_dtype, int M, int N, int K,
+                               long long lda, long long ldw, long long ldc, int batch, long long batch_a,
+                               long long batch_w, long long batch_c, cudaStream_t stream) {
+    return gemm_ref_launch(A, W, nullptr, C, in_dtype, out_dtype, M, N, K, lda, ldw, ldc, batch, batch_a, batch_w, batch_c, stream);
 }

@@ -356,10 +356,11 @@ __global__ void normed_add_rmsnorm_kernel(const TX* __restrict__ x, const float*
         ss += v * v;
     }
     if (out == nullptr) return;
-    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+    // without a scale for the second norm there is none: the sum itself goes out, in the output's type
+    const float inv = w ? 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps) : 1.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = keep ? row_s[i] : (rows == nullptr ? r[i] : r[i] + pb_ld(xr + i) * inv_x * wx[i]);
-        pb_st(out + i, v * inv * w[i]);
+        pb_st(out + i, w ? v * inv * w[i] : v);
     }
 }
 
@@ -421,13 +422,14 @@ __global__ void normed_add_rmsnorm_vec4_kernel(const TX* __restrict__ x, const f
         }
     }
     if (y == nullptr) return;
-    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+    const float inv = w ? 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps) : 1.0f;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
         const int i = threadIdx.x + it * blockDim.x;
         if (i < n4) {
-            const float4 v = rv[it], g = gw[it];
-            const float o0 = v.x * inv * g.x, o1 = v.y * inv * g.y, o2 = v.z * inv * g.z, o3 = v.w * inv * g.w;
+            const float4 v = rv[it], g = w ? gw[it] : make_float4(1.f, 1.f, 1.f, 1.f);
+            const float o0 = w ? v.x * inv * g.x : v.x, o1 = w ? v.y * inv * g.y : v.y, o2 = w ? v.z * inv * g.z : v.z,
+                        o3 = w ? v.w * inv * g.w : v.w;
             TY* out = y + row * width + 4 * (size_t)i;
             if constexpr (sizeof(TY) == 2) {
                 const __nv_bfloat162 p0 = __floats2bfloat162_rn(o0, o1), p1 = __floats2bfloat162_rn(o2, o3);
@@ -448,13 +450,13 @@ PB_API int pb_normed_add_rmsnorm(const void* x, const float* wx, float eps_x, fl
                                  int n_rows_total, const float* w, void* y, int dtype, int width, float eps,
                                  cudaStream_t stream) {
     PB_REQUIRE(n_out >= 0 && n_rows_total >= 0 && width > 0, "normed_add_rmsnorm: bad sizes");
-    PB_REQUIRE(x && wx && res && ((w == nullptr) == (y == nullptr)), "normed_add_rmsnorm: null pointer");
+    PB_REQUIRE(x && wx && res && (w == nullptr || y != nullptr), "normed_add_rmsnorm: null pointer");
     PB_REQUIRE(rows == nullptr ? n_out == n_rows_total : y != nullptr, "normed_add_rmsnorm: rows and outputs do not fit");
     if (n_out == 0) return 0;
     const int threads = norm_threads(width);
     const size_t esz = dtype == PB_BF16 ? 2 : 4;
     if (rows == nullptr && width % 4 == 0 && width <= 4 * threads * 8 && pb_aligned(x, 4 * esz) && pb_aligned(wx, 16) && pb_aligned(res, 16) &&
-        (w == nullptr || (pb_aligned(w, 16) && pb_aligned(y, 4 * esz)))) {
+        (w == nullptr || pb_aligned(w, 16)) && (y == nullptr || pb_aligned(y, 4 * esz))) {
         const int iters = (width / 4 + threads - 1) / threads;
 #define NA_VEC(IT)                                                                                                              \
     PB_DISPATCH_DTYPE(dtype, T, (pb_launch(normed_add_rmsnorm_vec4_kernel<T, T, IT>, dim3(n_out), dim3(threads), 0, stream, (const T*)x, wx, \

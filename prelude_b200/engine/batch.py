@@ -50,12 +50,14 @@ class StepItem:
 @dataclass
 class LayerCache:
     """What one entry of the run order reads and writes: pages of a cache
-    group, or per-request state, or nothing."""
-    kind: Optional[str] = None          # "kv" | "state" | None
+    group, or per-request state, or nothing; for a mixer made of several that each keep something, the members'
+    caches in ``children``."""
+    kind: Optional[str] = None          # "kv" | "state" | "combined" | None
     group: int = -1
     k_pages: Optional[torch.Tensor] = None     # [num_pages, n_kv_heads, page_size, head_dim]
     v_pages: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None       # [max_slots, *shape]
+    children: tuple = ()
 
 
 @dataclass

@@ -94,9 +94,10 @@ class Normed:
 
 
 def normed_add_rmsnorm(x: "Normed", res: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
-                       rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                       rows: Optional[torch.Tensor] = None, sum_out: bool = False) -> Optional[torch.Tensor]:
     """res += norm(x) (in place, unless ``rows`` picks rows: then res is left alone); returns rmsnorm(res) * weight
-    in ``out_dtype`` for every row, or for the chosen ones; with ``weight`` None only the sum is made."""
+    in ``out_dtype`` for every row, or for the chosen ones; with ``weight`` None only the sum is made, and with
+    ``sum_out`` it is also returned in ``out_dtype`` (for a sublayer that reads the stream itself)."""
     xt = x.x.materialize(out_dtype) if isinstance(x.x, PartialSums) else x.x
     _need(xt, "x", out_dtype)
     _need(x.weight, "x.weight", torch.float32)
@@ -113,6 +114,7 @@ def normed_add_rmsnorm(x: "Normed", res: torch.Tensor, weight: Optional[torch.Te
             raise KernelLibraryError("normed_add_rmsnorm: chosen rows need the norm that follows")
     if weight is not None:
         _need(weight, "weight", torch.float32)
+    if weight is not None or sum_out:
         out = torch.empty((n_out, width), dtype=out_dtype, device=res.device)
     check(_l.library().pb_normed_add_rmsnorm(xt.data_ptr(), x.weight.data_ptr(), x.eps, res.data_ptr(), _ptr(rows), n_out, total,
                                              _ptr(weight), _ptr(out), dtype_code(out_dtype), width, float(eps), _stream()),
@@ -594,4 +596,208 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, weights: torch.Tensor, out_dtype
     out = torch.empty((T, y.shape[1]), dtype=out_dtype, device=y.device)
     check(_l.library().pb_moe_combine(y.data_ptr(), dtype_code(y.dtype), plan.place_of.data_ptr(), weights.data_ptr(), out.data_ptr(),
                                       dtype_code(out_dtype), T, top, y.shape[1], _stream()), "moe_combine")
+    return out
+
+
+# -- mixers whose norm spans more than a head, rotation by rates, general paged attention ---------------------------
+def gemm_ref_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[b] = a[b] w[b]^T on the float32 units for a [B, M, K], w [B, N, K], out [B, M, N], each given as a view with
+    dense rows (the products' operands may interleave: a [tokens, heads, size] tensor seen heads first)."""
+    for t, name in ((a, "a"), (w, "w"), (out, "out")):
+        _need(t, name, contiguous=False)
+        if t.dim() != 3 or t.stride(2) != 1:
+            raise KernelLibraryError(f"gemm_ref_batched: {name} must be [batch, rows, cols] with dense rows")
+    B, M, Kd = a.shape
+    N = w.shape[1]
+    if w.shape != (B, N, Kd) or out.shape != (B, M, N) or w.dtype != a.dtype:
+        raise KernelLibraryError(f"gemm_ref_batched: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    check(_l.library().pb_gemm_ref_batched(a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(a.dtype), dtype_code(out.dtype),
+                                           M, N, Kd, a.stride(1), w.stride(1), out.stride(1), B, a.stride(0), w.stride(0),
+                                           out.stride(0), _stream()), "gemm_ref_batched")
+    return out
+
+
+def qkv_prepare(q_in: torch.Tensor, k_in: Optional[torch.Tensor], v_in: Optional[torch.Tensor], *, n_heads: int, q_dim: int,
+                q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, k_norm_cols: int = 0,
+                eps: float = 0.0, rates: Optional[torch.Tensor] = None, rot_dims: int = 0, adjacent: bool = False,
+                amplitude: float = 1.0, q_rot_off: int = 0, k_rot_off: int = 0, positions: torch.Tensor,
+                table_row: torch.Tensor, block_table: Optional[torch.Tensor] = None, q_out: torch.Tensor,
+                q_split: Optional[int] = None, q_out2: Optional[torch.Tensor] = None, q2_off: int = 0,
+                k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None, swizzle_k: bool = False,
+                swizzle_v: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Norm over whole projections, rotation by rates, queries to ``q_out`` (and their second part to ``q_out2``),
+    keys and values into pages; see csrc/qkv_prepare.cu.  ``q_in``, ``k_in``, ``v_in`` are [T, cols] views with dense
+    rows (columns of one merged projection); ``k_pages`` None: nothing is cached."""
+    T = q_in.shape[0]
+    dt = q_in.dtype
+    for t, name in ((q_in, "q_in"), (k_in, "k_in"), (v_in, "v_in")):
+        if t is not None:
+            _need(t, name, dt, contiguous=False)
+            if t.dim() != 2 or t.stride(1) != 1 or t.shape[0] != T:
+                raise KernelLibraryError(f"qkv_prepare: {name} must be [tokens, cols] with dense rows")
+    for t, name in ((q_weight, "q_weight"), (k_weight, "k_weight"), (rates, "rates")):
+        if t is not None:
+            _need(t, name, torch.float32)
+    _need(positions, "positions", torch.int32)
+    _need(table_row, "table_row", torch.int32)
+    q_split = q_dim if q_split is None else q_split
+    _need(q_out, "q_out", dt)
+    if q_in.shape[1] != n_heads * q_dim or q_out.numel() != T * n_heads * q_split:
+        raise KernelLibraryError(f"qkv_prepare: q_in {tuple(q_in.shape)}, q_out {tuple(q_out.shape)} for {n_heads} heads of {q_dim}")
+    if q_weight is not None and q_weight.numel() != n_heads * q_dim:
+        raise KernelLibraryError("qkv_prepare: the query norm's scale covers the whole projection")
+    if rates is not None and rates.numel() * 2 != rot_dims:
+        raise KernelLibraryError("qkv_prepare: one rate per rotated pair")
+    q2_stride = 0
+    if q_split < q_dim:
+        _need(q_out2, "q_out2", dt)
+        if q_out2.dim() != 3 or q_out2.shape[:2] != (T, n_heads) or q2_off + (q_dim - q_split) > q_out2.shape[2]:
+            raise KernelLibraryError(f"qkv_prepare: q_out2 {tuple(q_out2.shape)} has no room for {q_dim - q_split} elements from {q2_off}")
+        q2_stride = q_out2.shape[2]
+    G = kd = Gv = vd = page_size = num_pages = stride = 0
+    if k_pages is not None:
+        _need(k_pages, "k_pages", dt)
+        _need(block_table, "block_table", torch.int32)
+        num_pages, G, page_size, kd = k_pages.shape
+        stride = block_table.shape[1]
+        if k_in is None or k_in.shape[1] != G * kd:
+            raise KernelLibraryError(f"qkv_prepare: keys {None if k_in is None else tuple(k_in.shape)} against pages {tuple(k_pages.shape)}")
+        if k_weight is not None and k_weight.numel() < k_norm_cols:
+            raise KernelLibraryError("qkv_prepare: the key norm's scale is shorter than the columns it covers")
+        if v_pages is not None and v_pages.numel() > 0:
+            _need(v_pages, "v_pages", dt)
+            _, Gv, _, vd = v_pages.shape
+            if v_in is None or v_in.shape[1] != Gv * vd or v_pages.shape[0] != num_pages or v_pages.shape[2] != page_size:
+                raise KernelLibraryError(f"qkv_prepare: values against pages {tuple(v_pages.shape)}")
+        else:
+            v_pages = None
+    check(_l.library().pb_qkv_prepare(
+        q_in.data_ptr(), q_in.stride(0), _ptr(k_in), 0 if k_in is None else k_in.stride(0), _ptr(v_in),
+        0 if v_in is None else v_in.stride(0), dtype_code(dt), _ptr(q_weight), _ptr(k_weight), int(k_norm_cols), float(eps),
+        _ptr(rates), int(rot_dims), 1 if adjacent else 0, float(amplitude), int(q_rot_off), int(k_rot_off), positions.data_ptr(),
+        table_row.data_ptr(), _ptr(block_table), stride, page_size, num_pages, q_out.data_ptr(), q_split, _ptr(q_out2), q2_stride,
+        int(q2_off), _ptr(k_pages), _ptr(v_pages), T, n_heads, q_dim, G, kd, Gv, vd, 1 if swizzle_k else 0, 1 if swizzle_v else 0,
+        _ptr(status), _stream()), "qkv_prepare")
+    return q_out
+
+
+def attention_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[torch.Tensor], value_dim: int, positions: torch.Tensor,
+                    table_row: torch.Tensor, block_table: torch.Tensor, scale: float, window: Optional[int] = None,
+                    sink: Optional[torch.Tensor] = None, swizzle_k: bool = False, swizzle_v: bool = False,
+                    status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [T, H, kd] against pages [P, G, page, kd]; values from ``v_pages`` [P, Gv, page, value_dim], or, with
+    ``v_pages`` None, the first ``value_dim`` elements of the key rows.  float32 arithmetic; see csrc/attention_paged.cu."""
+    _need(q, "q")
+    _need(k_pages, "k_pages", q.dtype)
+    _need(positions, "positions", torch.int32)
+    _need(table_row, "table_row", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    T, H, kd = q.shape
+    num_pages, G, page_size, kd2 = k_pages.shape
+    if kd2 != kd:
+        raise KernelLibraryError(f"attention_paged: queries of {kd}, keys of {kd2}")
+    if v_pages is None:
+        vp, Gv, v_row = k_pages, G, kd
+        if value_dim > kd:
+            raise KernelLibraryError("attention_paged: values that are part of the keys cannot be longer than they")
+        swizzle_v = swizzle_k
+    else:
+        _need(v_pages, "v_pages", q.dtype)
+        vp, Gv, v_row = v_pages, v_pages.shape[1], v_pages.shape[3]
+        if v_row != value_dim or v_pages.shape[0] != num_pages or v_pages.shape[2] != page_size:
+            raise KernelLibraryError(f"attention_paged: value pages {tuple(v_pages.shape)} against key pages {tuple(k_pages.shape)}")
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
+        if sink.numel() != H:
+            raise KernelLibraryError("attention_paged: one sink per query head")
+    if out is None:
+        out = torch.empty((T, H, value_dim), dtype=q.dtype, device=q.device)
+    else:
+        _need(out, "out", q.dtype)
+        if tuple(out.shape) != (T, H, value_dim):
+            raise KernelLibraryError(f"attention_paged: out is {tuple(out.shape)}, the result {(T, H, value_dim)}")
+    check(_l.library().pb_attention_paged(
+        q.data_ptr(), k_pages.data_ptr(), vp.data_ptr(), out.data_ptr(), dtype_code(q.dtype), _ptr(sink), positions.data_ptr(),
+        table_row.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, num_pages, T, H, G, kd, value_dim, v_row, Gv,
+        float(scale), int(window or 0), 1 if swizzle_k else 0, 1 if swizzle_v else 0, _ptr(status), _stream()), "attention_paged")
+    return out
+
+
+# -- the state-space mixer ------------------------------------------------------------------------------------------
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, carried: torch.Tensor, batch,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(conv(x) + bias) per channel; x [T, C] a view with dense rows, weight float32 [C, taps], carried
+    [slots, taps - 1, C] of x's type (the sequences' last inputs of earlier steps)."""
+    _need(x, "x", contiguous=False)
+    _need(weight, "weight", torch.float32)
+    _need(bias, "bias", torch.float32)
+    _need(carried, "carried", x.dtype)
+    T, C = x.shape
+    taps = weight.shape[1]
+    if x.stride(1) != 1 or weight.shape[0] != C or bias.numel() != C or tuple(carried.shape[1:]) != (taps - 1, C):
+        raise KernelLibraryError(f"causal_conv_silu: x {tuple(x.shape)}, weight {tuple(weight.shape)}, carried {tuple(carried.shape)}")
+    if out is None:
+        out = torch.empty((T, C), dtype=x.dtype, device=x.device)
+    check(_l.library().pb_causal_conv_silu(x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr(), carried.data_ptr(),
+                                           out.data_ptr(), dtype_code(x.dtype), batch.token_seq.data_ptr(), batch.positions.data_ptr(),
+                                           batch.q_start.data_ptr(), batch.state_slots.data_ptr(), T, C, taps, _stream()),
+          "causal_conv_silu")
+    return out
+
+
+def conv_state_update(x: torch.Tensor, carried: torch.Tensor, batch) -> None:
+    """The last taps - 1 rows of x of every sequence of the step, into its slot of ``carried``."""
+    _need(x, "x", contiguous=False)
+    _need(carried, "carried", x.dtype)
+    check(_l.library().pb_conv_state_update(x.data_ptr(), x.stride(0), carried.data_ptr(), dtype_code(x.dtype), batch.cu_q.data_ptr(),
+                                            batch.state_slots.data_ptr(), batch.cu_q.numel() - 1, x.shape[1], carried.shape[1] + 1,
+                                            _stream()), "conv_state_update")
+
+
+def ssm_scan(u: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, batch, groups: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The recurrence over the step's tokens, sequence by sequence; u [T, heads * P + 2 * groups * N] dense, dt [T, heads] a
+    view with dense rows, state float32 [slots, heads, N, P]; returns y float32 [T, heads * P]."""
+    _need(u, "u")
+    _need(dt, "dt", u.dtype, contiguous=False)
+    for t, name in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip"), (state, "state")):
+        _need(t, name, torch.float32)
+    T = u.shape[0]
+    _, heads, N, P = state.shape
+    if u.shape[1] != heads * P + 2 * groups * N or tuple(dt.shape) != (T, heads) or dt.stride(1) != 1:
+        raise KernelLibraryError(f"ssm_scan: u {tuple(u.shape)}, dt {tuple(dt.shape)}, state {tuple(state.shape)}, {groups} groups")
+    if out is None:
+        out = torch.empty((T, heads * P), dtype=torch.float32, device=u.device)
+    check(_l.library().pb_ssm_scan(u.data_ptr(), dt.data_ptr(), dt.stride(0), dtype_code(u.dtype), dt_bias.data_ptr(), a_log.data_ptr(),
+                                   d_skip.data_ptr(), state.data_ptr(), out.data_ptr(), batch.cu_q.data_ptr(),
+                                   batch.state_slots.data_ptr(), batch.cu_q.numel() - 1, heads, P, N, groups, _stream()), "ssm_scan")
+    return out
+
+
+def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, parts: int, eps: float,
+                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y * silu(z) brought to unit root mean square in ``parts`` equal parts, times weight; y float32 [T, inner], z a view
+    [T, inner] with dense rows of the run's type, which the result has too."""
+    _need(y, "y", torch.float32)
+    _need(z, "z", contiguous=False)
+    _need(weight, "weight", torch.float32)
+    T, inner = y.shape
+    if tuple(z.shape) != (T, inner) or z.stride(1) != 1 or weight.numel() != inner:
+        raise KernelLibraryError(f"gated_group_rmsnorm: y {tuple(y.shape)}, z {tuple(z.shape)}")
+    if out is None:
+        out = torch.empty((T, inner), dtype=z.dtype, device=y.device)
+    check(_l.library().pb_gated_group_rmsnorm(y.data_ptr(), z.data_ptr(), z.stride(0), weight.data_ptr(), out.data_ptr(),
+                                              dtype_code(z.dtype), T, inner, parts, float(eps), _stream()), "gated_group_rmsnorm")
+    return out
+
+
+def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """sa * a + sb * b in float32, rounded once to ``out_dtype``."""
+    _need(a, "a")
+    _need(b, "b", a.dtype)
+    if a.shape != b.shape:
+        raise KernelLibraryError(f"scaled_sum: {tuple(a.shape)} against {tuple(b.shape)}")
+    out = torch.empty(a.shape, dtype=out_dtype, device=a.device)
+    check(_l.library().pb_scaled_sum(a.data_ptr(), float(sa), b.data_ptr(), float(sb), out.data_ptr(), dtype_code(a.dtype),
+                                     dtype_code(out_dtype), a.numel(), _stream()), "scaled_sum")
     return out

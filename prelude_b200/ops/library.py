@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 17
+ABI_VERSION = 18
 
 
 class KernelLibraryError(RuntimeError):
@@ -77,6 +77,15 @@ _SIGNATURES = {
     "pb_moe_gemv": ([P, L, P, I, P, L, I, I, I, P, P, P, I, P, L, I, P], I),
     "pb_moe_combine": ([P, I, P, P, P, I, I, I, I, P], I),
     "pb_moe_gather_rows": ([P, L, P, I, P, I, I, I, P], I),
+    "pb_gemm_ref_batched": ([P, P, P, I, I, I, I, I, L, L, L, I, L, L, L, P], I),
+    "pb_qkv_prepare": ([P, L, P, L, P, L, I, P, P, I, F, P, I, I, F, I, I, P, P, P, I, I, I, P, I, P, L, L, P, P, I, I, I, I, I, I, I,
+                        I, I, P, P], I),
+    "pb_attention_paged": ([P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P], I),
+    "pb_causal_conv_silu": ([P, L, P, P, P, P, I, P, P, P, P, I, I, I, P], I),
+    "pb_conv_state_update": ([P, L, P, I, P, P, I, I, I, P], I),
+    "pb_ssm_scan": ([P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P], I),
+    "pb_gated_group_rmsnorm": ([P, P, L, P, P, I, I, I, I, F, P], I),
+    "pb_scaled_sum": ([P, F, P, F, P, I, I, L, P], I),
     "pb_gemm_pair_grouped_bf16": ([P, P, P, I, I, I, I, L, L, L, I, P, P, P, I, I, P, P], I),
 }
 

@@ -251,3 +251,17 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             y += bias.to(y.dtype)
         return y
     raise KernelLibraryError(f"linear: unsupported type {x.dtype}")
+
+
+def batched_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[b] = a[b] w[b]^T for a [B, M, K], w [B, N, K] and out [B, M, N], all views with dense rows (the heads of a
+    [tokens, heads, size] tensor seen heads first): the float32 units in 32-bit, the library's strided batched
+    product in bfloat16."""
+    if a.dtype != w.dtype or out.dtype != a.dtype:
+        raise KernelLibraryError(f"batched_linear: a {a.dtype}, w {w.dtype}, out {out.dtype}")
+    if a.dtype == torch.float32:
+        return K.gemm_ref_batched(a, w, out)
+    if a.shape[1] == 0:
+        return out
+    torch.bmm(a, w.transpose(1, 2), out=out)
+    return out

@@ -102,3 +102,62 @@ class SandwichResidualBlock:
             return a
         x = self.ff_norm.add_forward(a, res)
         return self.ff_post_norm.pending(self.feed_forward.forward(x))
+
+
+@register_part("block", "postnorm_residual")
+class PostNormResidualBlock:
+    """Norms on the sublayers' outputs only; the sublayers read the residual stream itself:
+
+        res += delta ; a = mixer(res) ; res += norm1(a) ; f = ff(res) ; return norm2(f), pending
+
+    What arrives as ``delta`` is the previous block's output with its norm still to be applied
+    (``kernels.Normed``); one kernel norms it, adds it and hands the sum to the sublayer in the run's type (in
+    32-bit the sublayer reads the stream in place).  A block without a feed-forward returns its mixer's output
+    the same way."""
+
+    def __init__(self, spec: BlockSpec, prefix: str = ""):
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and spec.ff_post_norm is None):
+            raise ValueError("a post-norm block needs a norm after every sublayer it has")
+        self.spec = spec
+        p = spec.prefix
+        self.mixer = make_part("mixer", spec.mixer, f"{p}.{spec.mixer_name}")
+        self.mixer_post_norm = make_part("norm", spec.mixer_post_norm, f"{p}.{spec.mixer_post_norm_name}")
+        self.feed_forward = self.ff_post_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = make_part("feed_forward", spec.feed_forward, f"{p}.{spec.ff_name}")
+            self.ff_post_norm = make_part("norm", spec.ff_post_norm, f"{p}.{spec.ff_post_norm_name}")
+
+    def parts(self):
+        return tuple(x for x in (self.mixer, self.mixer_post_norm, self.feed_forward, self.ff_post_norm) if x is not None)
+
+    def tensors(self) -> Dict[str, TensorReq]:
+        out: Dict[str, TensorReq] = {}
+        for part in self.parts():
+            out.update(part.tensors())
+        return out
+
+    def load(self, get, ctx: RunContext) -> None:
+        self.dtype = ctx.dtype
+        for part in self.parts():
+            part.load(get, ctx)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def _stream(self, delta, res: torch.Tensor) -> torch.Tensor:
+        """res += delta (its pending norm applied); the stream in the type the sublayers read."""
+        from ..ops import kernels as K
+        if delta is None:
+            return res if self.dtype == torch.float32 else K.scaled_sum(res, 1.0, res, 0.0, self.dtype)
+        if not isinstance(delta, K.Normed):
+            raise TypeError("a post-norm block adds normed outputs to the stream")
+        x = K.normed_add_rmsnorm(delta, res, None, 0.0, self.dtype, sum_out=self.dtype != torch.float32)
+        return res if x is None else x
+
+    def forward(self, delta, res: torch.Tensor, batch, cache, write_cache: bool):
+        x = self._stream(delta, res)
+        a = self.mixer_post_norm.pending(self.mixer.forward(x, batch, cache, write_cache))
+        if self.feed_forward is None:
+            return a
+        x = self._stream(a, res)
+        return self.ff_post_norm.pending(self.feed_forward.forward(x))

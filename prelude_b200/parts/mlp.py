@@ -32,19 +32,19 @@ class GatedMlp:
     def tensors(self) -> Dict[str, TensorReq]:
         s, p = self.spec, self.prefix
         return {
-            f"{p}.gate_proj.weight": TensorReq((s.intermediate_size, s.hidden_size)),
-            f"{p}.up_proj.weight": TensorReq((s.intermediate_size, s.hidden_size)),
-            f"{p}.down_proj.weight": TensorReq((s.hidden_size, s.intermediate_size)),
+            f"{p}.{s.gate_name}": TensorReq((s.intermediate_size, s.hidden_size)),
+            f"{p}.{s.up_name}": TensorReq((s.intermediate_size, s.hidden_size)),
+            f"{p}.{s.down_name}": TensorReq((s.hidden_size, s.intermediate_size)),
         }
 
     def load(self, get, ctx: RunContext) -> None:
-        p = self.prefix
+        s, p = self.spec, self.prefix
 
         def mat(name):
             return get(f"{p}.{name}").to(device=ctx.device, dtype=ctx.dtype)
 
-        self.w_gate_up = torch.cat([mat("gate_proj.weight"), mat("up_proj.weight")], dim=0).contiguous()
-        self.w_down = mat("down_proj.weight").contiguous()
+        self.w_gate_up = torch.cat([mat(s.gate_name), mat(s.up_name)], dim=0).contiguous()
+        self.w_down = mat(s.down_name).contiguous()
 
     def activation_bytes_per_token(self, elem: int) -> int:
         """The merged gate/up projection, the activation, the output (as float32 partial sums at most)."""

@@ -21,11 +21,15 @@ from . import attention as _attention  # noqa: F401  (registers the part)
 from . import block as _block  # noqa: F401
 from . import diff_attention as _diff_attention  # noqa: F401
 from . import ends as _ends  # noqa: F401
+from . import gqa as _gqa  # noqa: F401
+from . import latent_attention as _latent_attention  # noqa: F401
+from . import parallel as _parallel  # noqa: F401
+from . import state_space as _state_space  # noqa: F401
 from . import mlp as _mlp  # noqa: F401
 from . import moe as _moe  # noqa: F401
 from . import norm as _norm  # noqa: F401
 from . import rope as _rope  # noqa: F401
-from .registry import KvPagesNeed, RunContext, RuntimeCaps, StateNeed, capturable, make_part
+from .registry import KvPagesNeed, RunContext, RuntimeCaps, StateNeed, capturable, leaf_needs, make_part
 
 
 class DecoderModel:
@@ -72,7 +76,7 @@ class DecoderModel:
 
     def runtime_caps(self) -> RuntimeCaps:
         """What the engine may do with this model, from what its parts say."""
-        needs = self.cache_needs()
+        needs = [leaf for top in self.cache_needs() for _, leaf in leaf_needs(top)]
         pages = any(isinstance(n, KvPagesNeed) for n in needs)
         return RuntimeCaps(kv_cache=pages, paged_attention=pages, varlen=True,
                            state_slots=any(isinstance(n, StateNeed) for n in needs),

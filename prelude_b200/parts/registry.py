@@ -15,7 +15,7 @@ Families and the calls the model makes on their members:
                 mixer reads ``cos`` and ``sin`` (float32 [positions, rotary_dim / 2], or
                 None: no rotation), ``rotary_dim``, and ``interleaved`` (absent or False:
                 angle j turns elements j and j + rotary_dim / 2; True: 2 j and 2 j + 1).
-  mixer         ``cache_need() -> KvPagesNeed | StateNeed | None`` and
+  mixer         ``cache_need() -> KvPagesNeed | StateNeed | CombinedNeed | None`` and
                 ``forward(x, batch, cache, write_cache) -> y`` with x, y [T, hidden].
   feed_forward  ``forward(x) -> y``.
   block         ``forward(delta, res, batch, cache, write_cache) -> delta'``: ``res``
@@ -130,6 +130,25 @@ class KvPagesNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A mixer that keeps one tensor of fixed ``shape`` per request."""
+    """A mixer that keeps one tensor of fixed ``shape`` per request; ``dtype`` None: the run's type."""
     shape: Tuple[int, ...]
-    dtype: torch.dtype = torch.float32
+    dtype: Optional[torch.dtype] = torch.float32
+
+
+@dataclass(frozen=True)
+class CombinedNeed:
+    """A mixer made of several that each keep something: one need per member (itself a ``KvPagesNeed``, a
+    ``StateNeed``, a ``CombinedNeed`` or None), in the members' order.  The mixer's cache is then a ``LayerCache``
+    whose ``children`` are the members' caches in that order."""
+    parts: Tuple[object, ...]
+
+
+def leaf_needs(need, path: Tuple[int, ...] = ()):
+    """(path, leaf need) of every ``KvPagesNeed`` and ``StateNeed`` inside a need, depth first."""
+    if need is None:
+        return
+    if isinstance(need, CombinedNeed):
+        for i, part in enumerate(need.parts):
+            yield from leaf_needs(part, path + (i,))
+    else:
+        yield path, need

@@ -47,6 +47,10 @@ def random_tensors(config: Union[dict, object], seed: int = 0, std: float = 0.02
             t = 1.0 + (torch.rand(req.shape, generator=g, dtype=torch.float32, device=device) * 2.0 - 1.0) * norm_jitter
         elif req.role == "norm_zero":       # a scale stored around zero
             t = (torch.rand(req.shape, generator=g, dtype=torch.float32, device=device) * 2.0 - 1.0) * norm_jitter
+        elif req.role == "conv":            # taps of a short convolution: of the order of one over their number
+            t = torch.randn(req.shape, generator=g, dtype=torch.float32, device=device) * (1.0 / max(1, req.shape[-1]) ** 0.5)
+        elif req.role == "log_rate":        # logarithm of a decay rate: rates between about 0.4 and 2.7
+            t = torch.rand(req.shape, generator=g, dtype=torch.float32, device=device) * 2.0 - 1.0
         elif req.role == "vector":          # a small vector whose products with its like enter an exponential
             t = torch.randn(req.shape, generator=g, dtype=torch.float32, device=device) * (0.5 / max(1, req.shape[0]) ** 0.5)
         else:
