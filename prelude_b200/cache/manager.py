@@ -312,6 +312,18 @@ class CacheManager:
             for t in self.state_tensors.values():
                 t.index_fill_(0, idx, 0)
 
+    def snapshot_state(self, slots: torch.Tensor):
+        """The state that the given slots (int32, on the device, each once) hold in every state tensor: what
+        ``restore_state`` puts back.  A step that is run twice on the same inputs (the warm-up before a capture)
+        is undone with it, since a recurrent state, unlike keys and values, is not the same after the second run."""
+        idx = slots.to(torch.long)
+        return idx, [t.index_select(0, idx) for t in self.state_tensors.values()]
+
+    def restore_state(self, snapshot) -> None:
+        idx, saved = snapshot
+        for t, s in zip(self.state_tensors.values(), saved):
+            t.index_copy_(0, idx, s)
+
     # -- accounting -------------------------------------------------------------------
     def free_pages(self) -> int:
         """Free pages in the tightest group."""

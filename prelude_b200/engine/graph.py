@@ -96,6 +96,9 @@ class DecodeGraph:
         """Warm up once eagerly on the current buffer contents, then capture."""
         from ..ops import library
         saved = self.buf.clone()
+        # the warm-up runs the step once for real: keys and values are written again by the replay with the same
+        # numbers, but per-request state (a recurrence) would be moved on twice, so it is put back
+        state = self.runner.cache.snapshot_state(self.slots) if self.runner.cache.state_tensors else None
         stream = torch.cuda.Stream(device=self.runner.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
@@ -103,6 +106,8 @@ class DecodeGraph:
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
         self.buf.copy_(saved)           # a self-feeding warm-up has moved tokens, positions and counters
+        if state is not None:
+            self.runner.cache.restore_state(state)
         before = library.launch_count
         graph = torch.cuda.CUDAGraph()
         with no_collection(), torch.cuda.graph(graph):
