@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 18
+ABI_VERSION = 19
 
 
 class KernelLibraryError(RuntimeError):
@@ -81,6 +81,10 @@ _SIGNATURES = {
     "pb_qkv_prepare": ([P, L, P, L, P, L, I, P, P, I, F, P, I, I, F, I, I, P, P, P, I, I, I, P, I, P, L, L, P, P, I, I, I, I, I, I, I,
                         I, I, P, P], I),
     "pb_attention_paged": ([P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P], I),
+    "pb_attention_paged_tc_supported": ([I, I, I, I, I], I),
+    "pb_attention_paged_tc_tile_tokens": ([I, I], I),
+    "pb_attention_paged_tc_scratch_floats": ([I, I, I, I], L),
+    "pb_attention_paged_tc_bf16": ([P, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, P, P], I),
     "pb_causal_conv_silu": ([P, L, P, P, P, P, I, P, P, P, P, I, I, I, P], I),
     "pb_conv_state_update": ([P, L, P, I, P, P, I, I, I, P], I),
     "pb_ssm_scan": ([P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P], I),

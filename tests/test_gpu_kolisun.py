@@ -429,3 +429,50 @@ def test_command_line_generates_from_a_kolisun_folder(folders):
     for _ in range(5):
         seq.append(int(plain.forward(cfg, w, seq, torch.float64)[-1].argmax()))
     assert json.loads(out.stdout.strip().splitlines()[0])["token_ids"] == seq[4:]
+
+
+# -- the tensor-core general attention kernel against the plain kernel ----------------------------------------------------
+@pytest.mark.parametrize("heads,kv,kd,vd,shared,page,window,sink", [
+    (16, 1, 576, 512, True, 16, None, True), (6, 1, 112, 96, True, 16, None, True), (8, 2, 64, 128, False, 16, 100, False),
+    (4, 4, 48, 96, False, 8, None, True), (128, 1, 96, 64, True, 32, None, False), (5, 1, 32, 32, True, 16, 33, True),
+    (4, 2, 128, 64, False, 64, 700, False), (64, 2, 160, 160, True, 16, None, True)])
+def test_tensor_core_general_attention_equals_the_plain_kernel(heads, kv, kd, vd, shared, page, window, sink):
+    """Random keys and values in scattered pages; requests of unequal length: long portions, a portion of two tokens,
+    single tokens far into a long context (their keys dealt to several blocks), with and without a window and a sink;
+    then a step of single tokens only.  Both kernels read the same pages."""
+    from prelude_b200.cache.manager import CacheManager
+    from prelude_b200.engine.batch import StepItem, build_step_batch
+    from prelude_b200.ops import kernels as K
+    from prelude_b200.ops import paged_general as G
+    from prelude_b200.parts.registry import KvPagesNeed
+    dev = torch.device(DEV)
+    g = torch.Generator().manual_seed(heads * 31 + kd)
+    need = KvPagesNeed(kv, kd, window, v_heads=0, v_head_dim=0) if shared else KvPagesNeed(kv, kd, window, v_heads=kv, v_head_dim=vd)
+    sinks = torch.linspace(-1.0, 3.0, heads).to(dev) if sink else None
+    mixed = [(0, 150), (700, 2), (1500, 1), (130, 70), (63, 1)]
+    decode = [(1900, 1), (5, 1), (640, 1)]
+    for shape in (mixed, decode):
+        cache = CacheManager([need], page, sum(-(-(a + b) // page) for a, b in shape) + 3, 8, dev, torch.bfloat16)
+        items, slots = [], []
+        for i, (have, new) in enumerate(shape):
+            cache.add_request(i)
+            cache.grow(i, have + new)
+            items.append(StepItem(i, [0] * new, have, []))
+            slots.append(cache.slot_of(i))
+        lc = cache.layer_cache(0)
+        lc.k_pages.copy_(torch.randn(lc.k_pages.shape, generator=g).to(dev, torch.bfloat16))
+        v_pages = None
+        if not shared:
+            lc.v_pages.copy_(torch.randn(lc.v_pages.shape, generator=g).to(dev, torch.bfloat16))
+            v_pages = lc.v_pages
+        batch = build_step_batch(items, cache.block_tables(list(range(len(shape)))), slots, dev, 10, 1 << 20)
+        q = (torch.randn(batch.n_tokens, heads, kd, generator=g) * 1.5).to(dev, torch.bfloat16)
+        scale = 1.0 / math.sqrt(kd)
+        assert G.tc_takes(q, lc.k_pages, v_pages, vd)
+        got = G.attention_general(q, lc.k_pages, v_pages, vd, batch, 0, scale, window, sinks).float()
+        want = K.attention_paged(q, lc.k_pages, v_pages, vd, batch.positions, batch.table_row_of_token, batch.block_tables[0], scale,
+                                 window, sinks, status=batch.status).float()
+        assert int(batch.status.item()) == 0
+        err = (got - want).abs()
+        assert float(err.max()) < 4e-2 * float(want.abs().max()) and float(err.mean()) < 4e-3 * float(want.abs().max()), \
+            (float(err.max()), float(err.mean()), float(want.abs().max()))
