@@ -489,6 +489,177 @@ def pabelix_compare(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --workload kolisun: the Kolisun design beside Qwen3 dense at equal layer sizes
+# ---------------------------------------------------------------------------------------------------------------
+KOLISUN_SIZES = {
+    # width; window attention: heads, key/value heads, head size, window; state-space mixer: heads, head size, state, groups;
+    # latent attention: heads, plain and rotated query/key sizes, value size, latent sizes; feed-forward width.
+    # Qwen3 at the same width has the window attention's heads and head size and the same feed-forward width.
+    "2k": dict(width=2048, heads=16, kv=4, dim=128, window=1024, ss_heads=64, ss_dim=64, state=128, groups=8,
+               lat_heads=16, lat_dim=128, rot=64, vdim=128, kv_rank=512, q_rank=1536, ff=8192),
+    "4k": dict(width=4096, heads=32, kv=8, dim=128, window=1024, ss_heads=128, ss_dim=64, state=128, groups=8,
+               lat_heads=32, lat_dim=128, rot=64, vdim=128, kv_rank=512, q_rank=1536, ff=12288),
+}
+
+
+def kolisun_config(z, layers, vocab):
+    """Layers that resemble a real model's: one layer with window attention and a state-space mixer side by side, then two
+    with latent attention, and so on; every layer with a SiLU-gated feed-forward."""
+    par = {"left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                    "mask": {"size": z["window"]},
+                    "rot": {"dims": z["dim"], "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+           "right": {"heads": z["ss_heads"], "vdim": z["ss_dim"], "state": z["state"], "groups": z["groups"], "conv": 4, "norm_groups": z["groups"]},
+           "left_scale": 1.0, "right_scale": 1.0}
+    lat = {"heads": z["lat_heads"], "dim": z["lat_dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
+           "scale": (z["lat_dim"] + z["rot"]) ** -0.5,
+           "rot": {"dims": z["rot"], "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    out = [{"type": "parallel", "mixer": par, "mlp": mlp} if i % 3 == 0 else {"type": "latent_attention", "mixer": lat, "mlp": mlp}
+           for i in range(layers)]
+    return {"architecture": "Kolisun", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6}, "layers": out}
+
+
+def kolisun_kernels(pk, size):
+    """The new design's kernels beside their like of the closest model, one launch each: latent attention over a prompt of
+    2,048 tokens and for 8 decoded tokens at 2,048 keys beside Qwen3's attention kernels; the kernel between projection and
+    attention beside Qwen3's; the state-space mixer's kernels against the bytes they must move."""
+    import torch
+    from prelude_b200.cache.manager import CacheManager
+    from prelude_b200.engine.batch import StepItem, build_step_batch
+    from prelude_b200.ops import kernels as K
+    from prelude_b200.ops.attention import paged_attention
+    from prelude_b200.ops.paged_general import attention_general
+    from prelude_b200.parts.registry import CombinedNeed, KvPagesNeed, StateNeed
+    z = KOLISUN_SIZES[size]
+    dev = torch.device("cuda:0")
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)
+    bf = torch.bfloat16
+    out = {}
+    T, ctx, B = 2048, 2048, 8
+    H, G, D = z["heads"], z["kv"], z["dim"]
+    LH, row, rank = z["lat_heads"], z["kv_rank"] + z["rot"], z["kv_rank"]
+    SH, P, N, SG = z["ss_heads"], z["ss_dim"], z["state"], z["groups"]
+    inner, channels = SH * P, SH * P + 2 * SG * N
+    needs = [KvPagesNeed(1, row, None, 0, 0), KvPagesNeed(G, D),
+             CombinedNeed((StateNeed((SH, N, P), torch.float32), StateNeed((3, channels), None)))]
+    cache = CacheManager(needs, PAGE_SIZE, (B * (ctx + 16) + T) // PAGE_SIZE + 8, B + 1, dev, bf)
+    lat, plain = cache.layer_cache(0), cache.layer_cache(1)
+    lat.k_pages.normal_()
+    plain.k_pages.normal_()
+    plain.v_pages.normal_()
+    sink = torch.zeros(LH, device=dev)
+    # -- one request of T prompt tokens
+    cache.add_request("p")
+    cache.grow("p", T)
+    batch = build_step_batch([StepItem("p", [0] * T, 0, [])], cache.block_tables(["p"]), [cache.slot_of("p")], dev, 10, 1 << 20)
+    cache.zero_fresh_state()
+    pairs = T * (T + 1) // 2
+    q = torch.randn(T, LH, row, device=dev).to(bf)
+    ms = _event_ms(lambda: attention_general(q, lat.k_pages, None, rank, batch, cache.group_of[0], row ** -0.5, None, sink), flush=flush)
+    out["prefill_attention"] = {"latent_ms": round(ms, 4), "latent_tflops": round(2 * LH * pairs * (row + rank) / ms / 1e9, 1)}
+    q3 = torch.randn(T, H, D, device=dev).to(bf)
+    ms = _event_ms(lambda: paged_attention(q3, plain.k_pages, plain.v_pages, batch, cache.group_of[1], D ** -0.5, None), flush=flush)
+    out["prefill_attention"].update(qwen3_ms=round(ms, 4), qwen3_tflops=round(H * pairs * 4 * D / ms / 1e9, 1))
+    # the kernel between projection and attention
+    proj = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+    wq, wk = torch.ones(H * D, device=dev), torch.ones(G * D, device=dev)
+    rates = torch.rand(D // 2, device=dev)
+    qo = torch.empty(T, H, D, dtype=bf, device=dev)
+    ms = _event_ms(lambda: K.qkv_prepare(proj[:, :H * D], proj[:, H * D:(H + G) * D], proj[:, (H + G) * D:], n_heads=H, q_dim=D, q_weight=wq,
+                                         k_weight=wk, k_norm_cols=G * D, eps=1e-6, rates=rates, rot_dims=D, adjacent=True,
+                                         positions=batch.positions, table_row=batch.table_row_of_token,
+                                         block_table=batch.block_tables[cache.group_of[1]], q_out=qo, k_pages=plain.k_pages,
+                                         v_pages=plain.v_pages, swizzle_k=True, swizzle_v=True, status=batch.status), flush=flush)
+    moved = T * (H + 2 * G) * D * 2 * 2
+    out["projection_to_pages"] = {"kolisun_us": round(ms * 1e3, 2), "kolisun_gbs": round(moved / ms / 1e6, 1)}
+    ang = torch.arange(T, device=dev, dtype=torch.float32).reshape(-1, 1) * rates.reshape(1, -1)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    hw = torch.ones(D, device=dev)
+    ms = _event_ms(lambda: K.qknorm_rope_kvwrite(proj, H, G, D, hw, hw, 1e-6, cos, sin, D, batch.positions, batch.table_row_of_token,
+                                                 batch.block_tables[cache.group_of[1]], plain.k_pages, plain.v_pages, True, batch.status,
+                                                 out=qo), flush=flush)
+    out["projection_to_pages"].update(qwen3_us=round(ms * 1e3, 2), qwen3_gbs=round(moved / ms / 1e6, 1))
+    # the state-space mixer's kernels over the prompt
+    sc = cache.layer_cache(2)
+    state, carried = sc.children[0].state, sc.children[1].state
+    sproj = (torch.randn(T, 2 * inner + 2 * SG * N + SH, device=dev) * 0.5).to(bf)
+    xbc, dt, zz = sproj[:, inner:inner + channels], sproj[:, inner + channels:], sproj[:, :inner]
+    conv_w, conv_b = torch.randn(channels, 4, device=dev) * 0.5, torch.zeros(channels, device=dev)
+    hb, al, dd, nw = torch.zeros(SH, device=dev), torch.zeros(SH, device=dev), torch.ones(SH, device=dev), torch.ones(inner, device=dev)
+    u = K.causal_conv_silu(xbc, conv_w, conv_b, carried, batch)
+    y = K.ssm_scan(u, dt, hb, al, dd, state, batch, SG)
+    ms_c = _event_ms(lambda: K.causal_conv_silu(xbc, conv_w, conv_b, carried, batch, out=u), flush=flush)
+    ms_s = _event_ms(lambda: K.ssm_scan(u, dt, hb, al, dd, state, batch, SG, out=y), flush=flush)
+    ms_n = _event_ms(lambda: K.gated_group_rmsnorm(y, zz, nw, SG, 1e-6), flush=flush)
+    out["state_space_prefill"] = {
+        "conv_us": round(ms_c * 1e3, 2), "conv_gbs": round(T * channels * 2 * 2 / ms_c / 1e6, 1),
+        "scan_us": round(ms_s * 1e3, 2), "scan_gbs": round((T * channels * 2 + T * inner * 4) / ms_s / 1e6, 1),
+        "scan_gflops": round(T * SH * N * P * 6 / ms_s / 1e6, 1),
+        "gated_norm_us": round(ms_n * 1e3, 2), "gated_norm_gbs": round(T * inner * (4 + 2 + 2) / ms_n / 1e6, 1)}
+    cache.release("p")
+    # -- B single tokens at ctx keys
+    rids = [f"d{i}" for i in range(B)]
+    for r in rids:
+        cache.add_request(r)
+        cache.grow(r, ctx + 1)
+    batch = build_step_batch([StepItem(r, [0], ctx, []) for r in rids], cache.block_tables(rids), [cache.slot_of(r) for r in rids], dev, 10, 1 << 20)
+    cache.zero_fresh_state()
+    q = torch.randn(B, LH, row, device=dev).to(bf)
+    ms = _event_ms(lambda: attention_general(q, lat.k_pages, None, rank, batch, cache.group_of[0], row ** -0.5, None, sink), flush=flush, reps=20)
+    out["decode_attention"] = {"latent_us": round(ms * 1e3, 2), "latent_gbs": round(B * (ctx + 1) * row * 2 / ms / 1e6, 1)}
+    q3 = torch.randn(B, H, D, device=dev).to(bf)
+    ms = _event_ms(lambda: paged_attention(q3, plain.k_pages, plain.v_pages, batch, cache.group_of[1], D ** -0.5, None), flush=flush, reps=20)
+    out["decode_attention"].update(qwen3_us=round(ms * 1e3, 2), qwen3_gbs=round(B * (ctx + 1) * G * 2 * D * 2 / ms / 1e6, 1))
+    u8, y8 = u[:B], y[:B]
+    ms_s = _event_ms(lambda: K.ssm_scan(u8, dt[:B], hb, al, dd, state, batch, SG, out=y8), flush=flush, reps=20)
+    out["state_space_decode"] = {"scan_us": round(ms_s * 1e3, 2), "scan_state_gbs": round(B * SH * N * P * 4 * 2 / ms_s / 1e6, 1)}
+    out["peaks"] = {"bf16_tflops": pk["bf16_tflops"], "hbm_gbs": pk["hbm_gbs"], "source": pk["source"]}
+    return out
+
+
+def kolisun_compare(args):
+    """Prefill and decode throughput of Kolisun beside Qwen3 dense at equal layer sizes (random weights, bfloat16):
+    one prompt of --prefill-tokens through the step function, and --batch requests decoding behind --prefix-len
+    tokens on the captured step, both timed on the device.  One JSON line of its own."""
+    import torch
+    pk = peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    t_begin = time.time()
+    points = []
+    vocab = 32768
+    for size in args.sizes.split(","):
+        z = KOLISUN_SIZES[size]
+        layers = args.layers or 6
+        arms = {
+            "kolisun": kolisun_config(z, layers, vocab),
+            "qwen3": dict(QWEN3_4B, vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=layers,
+                          num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["dim"], tie_word_embeddings=True),
+        }
+        point = {"size": size, "layers": layers, "width": z["width"]}
+        for name, cfg in arms.items():
+            pages_per_req = -(-(PREFIX_LEN + args.warmup + args.steps + 2) // PAGE_SIZE)
+            engine = _engine_for(cfg, args.batch * pages_per_req + 2 * (PREFILL_TOKENS // PAGE_SIZE) + 8, args.batch + 2)
+            shim = {"vocab_size": vocab}
+            prefill_ms, _ = time_prefill(engine, shim, args.warmup)
+            dec, _ = time_decode(engine, shim, args.batch, args.steps, args.warmup, seed=1)
+            point[name] = {"prefill_tok_s": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                           "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms_per_step"], 4),
+                           "weight_gb": round(engine.model.weight_bytes() / 1e9, 3)}
+            del engine
+            torch.cuda.empty_cache()
+        point["kernels"] = kolisun_kernels(pk, size)
+        points.append(point)
+    clocks.stop()
+    print(json.dumps({"metric": "Kolisun beside Qwen3 dense at equal layer sizes: prefill and decode tokens a second, device-timed",
+                      "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "steps": args.steps,
+                      "warmup": args.warmup, "config": {"batch": args.batch, "prefix_len": PREFIX_LEN, "prefill_tokens": PREFILL_TOKENS,
+                                                        "page_size": PAGE_SIZE, "l2": "inputs_exceed_l2 (steps), flushed (kernels)"},
+                      "points": points, "clocks": clocks.summary([(t_begin, time.time())])}))
+    return 0
+
+
 def serve(args):
     """A mixed continuous batch through ``Engine.generate`` (host tokens in, host tokens out): ``--requests`` prompts
     of uniform random ids with lengths uniform in [128, 2048], prompts cut into portions of ``--prefill-chunk``
@@ -553,10 +724,10 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels' timeline of one layer of the decode step to stderr (needs PRELUDE_TIMELINE=1 in the environment)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "pabelix"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "pabelix", "kolisun"],
                     help="serving: a mixed continuous batch through Engine.generate instead of the decode step (a line of its own); "
-                         "pabelix: the Pabelix design beside Qwen3 dense at equal layer sizes (a line of its own)")
-    ap.add_argument("--sizes", default="2k,4k", help="pabelix: which layer sizes to run (2k, 4k)")
+                         "pabelix, kolisun: that design beside Qwen3 dense at equal layer sizes (a line of its own)")
+    ap.add_argument("--sizes", default="2k,4k", help="pabelix, kolisun: which layer sizes to run (2k, 4k)")
     ap.add_argument("--requests", type=int, default=32, help="serving: number of requests")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: tokens per portion of a prompt")
     ap.add_argument("--new-tokens", type=int, default=256, help="serving: generated tokens per request")
@@ -584,6 +755,9 @@ def main():
     if args.workload == "pabelix":
         args.layers = 0 if args.layers == MODEL["num_hidden_layers"] else args.layers
         return pabelix_compare(args)
+    if args.workload == "kolisun":
+        args.layers = 0 if args.layers == MODEL["num_hidden_layers"] else args.layers
+        return kolisun_compare(args)
     import torch
     pk = peaks()
     # cache: the largest point (64 requests) with room for prefix + generated tokens, in whole pages

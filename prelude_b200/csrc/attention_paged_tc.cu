@@ -129,11 +129,15 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
     }
     __syncthreads();
     const int kchunks = kd >> 3, vchunks = vd >> 3;
-    for (int idx = tid; idx < TC_ROWS * kchunks; idx += 256) {
-        const int row = idx / kchunks, ch = idx - row * kchunks;
-        bf16* dst = Qs + row * ldk + ch * 8;
-        if (row_q[row] >= 0) cp_async16(dst, p.q + (size_t)row_q[row] * kd + ch * 8);
-        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    const int ld_row = tid >> 3, ld_sub = tid & 7;                         // eight threads copy a row, 16 bytes at a time
+    {
+        bf16* dst = Qs + ld_row * ldk;
+        if (row_q[ld_row] >= 0) {
+            const bf16* src = p.q + (size_t)row_q[ld_row] * kd;
+            for (int ch = ld_sub; ch < kchunks; ch += 8) cp_async16(dst + ch * 8, src + ch * 8);
+        } else {
+            for (int ch = ld_sub; ch < kchunks; ch += 8) *reinterpret_cast<uint4*>(dst + ch * 8) = make_uint4(0, 0, 0, 0);
+        }
     }
 
     const int row0 = r * 16 + (lane >> 2), row1 = row0 + 8;
@@ -147,22 +151,24 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
 
     for (int kt = kt_begin; kt < kt_end; ++kt) {
         const int kbase = kt * TC_KEYS;
-        for (int idx = tid; idx < TC_KEYS * kchunks; idx += 256) {
-            const int key = idx / kchunks, ch = idx - key * kchunks;
-            bf16* dst = Ks + key * ldk + ch * 8;
-            const int page = key_page[key];
-            const int j = kbase + key;
-            if (page >= 0) cp_async16(dst, p.k_pages + (((size_t)page * p.G + g) * p.page_size + j % p.page_size) * kd + ch * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-        }
-        if (!p.v_shared) {
-            for (int idx = tid; idx < TC_KEYS * vchunks; idx += 256) {
-                const int key = idx / vchunks, ch = idx - key * vchunks;
-                bf16* dst = Vs + key * ldv + ch * 8;
-                const int page = key_page[key];
-                const int j = kbase + key;
-                if (page >= 0) cp_async16(dst, p.v_pages + (((size_t)page * p.G + g) * p.page_size + j % p.page_size) * p.v_row + ch * 8);
-                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        {
+            const int page = key_page[ld_row];
+            const int in_page = (kbase + ld_row) % p.page_size;
+            bf16* dst = Ks + ld_row * ldk;
+            if (page >= 0) {
+                const bf16* src = p.k_pages + (((size_t)page * p.G + g) * p.page_size + in_page) * kd;
+                for (int ch = ld_sub; ch < kchunks; ch += 8) cp_async16(dst + ch * 8, src + ch * 8);
+            } else {
+                for (int ch = ld_sub; ch < kchunks; ch += 8) *reinterpret_cast<uint4*>(dst + ch * 8) = make_uint4(0, 0, 0, 0);
+            }
+            if (!p.v_shared) {
+                bf16* vdst = Vs + ld_row * ldv;
+                if (page >= 0) {
+                    const bf16* src = p.v_pages + (((size_t)page * p.G + g) * p.page_size + in_page) * p.v_row;
+                    for (int ch = ld_sub; ch < vchunks; ch += 8) cp_async16(vdst + ch * 8, src + ch * 8);
+                } else {
+                    for (int ch = ld_sub; ch < vchunks; ch += 8) *reinterpret_cast<uint4*>(vdst + ch * 8) = make_uint4(0, 0, 0, 0);
+                }
             }
         }
         cp_async_wait_all();
@@ -170,14 +176,35 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
 
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         {
+            // four chains of products, one after the other in k: a single accumulator would make every product wait for
+            // the one before it
+            float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f}, s3[4] = {0.f, 0.f, 0.f, 0.f};
             const bf16* a_ptr = Qs + (r * 16 + (lane & 15)) * ldk + (lane >> 4) * 8;
             const bf16* b_ptr = Ks + (c * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8;
-            for (int kk = 0; kk < kd; kk += 16) {
+            int kk = 0;
+            for (; kk + 64 <= kd; kk += 64) {
+                unsigned a0[4], a1[4], a2[4], a3[4], b0[2], b1[2], b2[2], b3[2];
+                ldmatrix_x4(a0, a_ptr + kk);
+                ldmatrix_x2(b0, b_ptr + kk);
+                ldmatrix_x4(a1, a_ptr + kk + 16);
+                ldmatrix_x2(b1, b_ptr + kk + 16);
+                ldmatrix_x4(a2, a_ptr + kk + 32);
+                ldmatrix_x2(b2, b_ptr + kk + 32);
+                ldmatrix_x4(a3, a_ptr + kk + 48);
+                ldmatrix_x2(b3, b_ptr + kk + 48);
+                mma_bf16(s, a0, b0);
+                mma_bf16(s1, a1, b1);
+                mma_bf16(s2, a2, b2);
+                mma_bf16(s3, a3, b3);
+            }
+            for (; kk < kd; kk += 16) {
                 unsigned a[4], b[2];
                 ldmatrix_x4(a, a_ptr + kk);
                 ldmatrix_x2(b, b_ptr + kk);
                 mma_bf16(s, a, b);
             }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[e] = (s[e] + s1[e]) + (s2[e] + s3[e]);
         }
         const int pos0 = row_pos[row0], pos1 = row_pos[row1];
 #pragma unroll
@@ -268,27 +295,44 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
     }
 }
 
-// One block per (token, head): the parts of its key ranges, the sink, the division.
-__global__ void attention_paged_tc_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                                const float* __restrict__ sink, const int32_t* __restrict__ table_row,
-                                                bf16* __restrict__ out, int H, int vd, int splits) {
+// One block per (token, head): the parts of its key ranges, the sink, the division.  The parts' weights
+// exp(m_s - M) / L are made once, by the first warp; then every thread adds up its columns, the loads of all parts
+// in flight together.
+#define TC_MAX_SPLITS 64
+__global__ void __launch_bounds__(128) attention_paged_tc_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                                       const float* __restrict__ sink, const int32_t* __restrict__ table_row,
+                                                                       bf16* __restrict__ out, int H, int vd, int splits) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
+    __shared__ float w_s[TC_MAX_SPLITS];
     const int row = blockIdx.x;
     if (table_row[row / H] < 0) return;
-    const float* ml = part_ml + (size_t)row * splits * 2;
-    float M = sink ? sink[row % H] : -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
-    float L = sink ? expf(sink[row % H] - M) : 0.f;
-    for (int s = 0; s < splits; ++s) { const float m = ml[2 * s]; if (m != -INFINITY) L += ml[2 * s + 1] * expf(m - M); }
-    const float inv = L > 0.f ? 1.0f / L : 0.f;
-    for (int d = threadIdx.x; d < vd; d += blockDim.x) {
-        float acc = 0.f;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float* ml = part_ml + (size_t)row * splits * 2;
+        const float ma = lane < splits ? ml[2 * lane] : -INFINITY, mb = lane + 32 < splits ? ml[2 * (lane + 32)] : -INFINITY;
+        const float la = lane < splits ? ml[2 * lane + 1] : 0.f, lb = lane + 32 < splits ? ml[2 * (lane + 32) + 1] : 0.f;
+        const float sk = sink ? sink[row % H] : -INFINITY;
+        const float M = fmaxf(pb_warp_max(fmaxf(ma, mb)), sk);
+        const float wa = ma == -INFINITY ? 0.f : expf(ma - M), wb = mb == -INFINITY ? 0.f : expf(mb - M);
+        const float L = pb_warp_sum(la * wa + lb * wb) + (sink ? expf(sk - M) : 0.f);
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        w_s[lane] = wa * inv;
+        w_s[lane + 32] = wb * inv;
+    }
+    __syncthreads();
+    const float* po = part_o + (size_t)row * splits * vd;
+    for (int d = threadIdx.x * 4; d < vd; d += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
         for (int s = 0; s < splits; ++s) {
-            const float m = ml[2 * s];
-            if (m != -INFINITY) acc += part_o[((size_t)row * splits + s) * vd + d] * expf(m - M);
+            const float4 v = *reinterpret_cast<const float4*>(po + (size_t)s * vd + d);
+            const float w = w_s[s];
+            acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y); acc.z = fmaf(v.z, w, acc.z); acc.w = fmaf(v.w, w, acc.w);
         }
-        out[(size_t)row * vd + d] = __float2bfloat16_rn(acc * inv);
+        bf16* o = out + (size_t)row * vd + d;
+        *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(acc.x, acc.y);
+        *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(acc.z, acc.w);
     }
 }
 
@@ -329,7 +373,7 @@ PB_API int pb_attention_paged_tc_bf16(const void* q, const void* k_pages, const 
     PB_REQUIRE(q && k_pages && v_pages && out && positions && table_row && block_table, "attention_paged_tc: null pointer");
     PB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0 && n_tiles >= 0 && n_tokens >= 0, "attention_paged_tc: bad geometry");
     PB_REQUIRE(tile_seq == nullptr || (tile_tok0 && cu_q), "attention_paged_tc: a list of tiles needs the portions' offsets");
-    PB_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || scratch), "attention_paged_tc: %d splits", splits);
+    PB_REQUIRE(splits >= 1 && splits <= TC_MAX_SPLITS && (splits == 1 || (scratch && pb_aligned(scratch, 16))), "attention_paged_tc: %d splits", splits);
     PB_REQUIRE(pb_aligned(q, 16) && pb_aligned(k_pages, 16) && pb_aligned(v_pages, 16) && pb_aligned(out, 4) && (v_shared || v_row % 8 == 0),
                "attention_paged_tc: operands must be 16-byte aligned");
     if (n_tiles == 0) return 0;

@@ -39,7 +39,7 @@ struct RotArgs {
 
 // element d of a head whose rotated span starts at `off`: its value after norm and rotation
 template <typename T>
-__device__ __forceinline__ float rotated(const T* head, const float* w_head, float inv, int d, int off, const RotArgs& r, float pos) {
+__device__ __forceinline__ float rotated(const T* head, const float* w_head, float inv, int d, int off, const RotArgs& r, const float* cs) {
     const float own = pb_ld(head + d) * inv * (w_head ? w_head[d] : 1.0f);
     const int rel = d - off;
     if (r.rates == nullptr || rel < 0 || rel >= r.dims) return own;
@@ -49,10 +49,7 @@ __device__ __forceinline__ float rotated(const T* head, const float* w_head, flo
     if (r.adjacent) { i = rel >> 1; first = (rel & 1) == 0; partner = first ? d + 1 : d - 1; }
     else { first = rel < half; i = first ? rel : rel - half; partner = first ? d + half : d - half; }
     const float other = pb_ld(head + partner) * inv * (w_head ? w_head[partner] : 1.0f);
-    float s, c;
-    sincosf(pos * r.rates[i], &s, &c);
-    s *= r.amplitude;
-    c *= r.amplitude;
+    const float c = cs[2 * i], s = cs[2 * i + 1];          // of this token's angle i, made once per token
     return first ? own * c - other * s : own * c + other * s;
 }
 
@@ -68,11 +65,20 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, long long ldq, co
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     __shared__ float red[32];
+    extern __shared__ float cs[];                          // cosine and sine of the token's angles, times the amplitude
     const int t = blockIdx.x;
     const int row = table_row[t];
     if (row < 0) return;
     const int p = positions[t];
-    const float pos = (float)p;
+    if (rot.rates != nullptr) {
+        for (int i = threadIdx.x; i < rot.dims / 2; i += blockDim.x) {
+            float sn, c;
+            sincosf((float)p * rot.rates[i], &sn, &c);
+            cs[2 * i] = c * rot.amplitude;
+            cs[2 * i + 1] = sn * rot.amplitude;
+        }
+        __syncthreads();
+    }
     const T* q = q_in + (size_t)t * ldq;
     float inv_q = 1.0f, inv_k = 1.0f;
     if (q_w != nullptr) {
@@ -82,7 +88,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, long long ldq, co
     }
     for (int i = threadIdx.x; i < H * qd; i += blockDim.x) {
         const int h = i / qd, d = i - h * qd;
-        const float v = rotated(q + (size_t)h * qd, q_w ? q_w + (size_t)h * qd : nullptr, inv_q, d, q_rot_off, rot, pos);
+        const float v = rotated(q + (size_t)h * qd, q_w ? q_w + (size_t)h * qd : nullptr, inv_q, d, q_rot_off, rot, cs);
         if (d < q_split) pb_st(q_out + ((size_t)t * H + h) * q_split + d, v);
         else pb_st(q_out2 + ((size_t)t * H + h) * q2_head_stride + q2_off + (d - q_split), v);
     }
@@ -104,7 +110,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, long long ldq, co
         // the norm covers the first k_norm_cols elements of the projection; the span a rotation turns lies wholly
         // inside or wholly outside them (the launcher checks)
         const bool normed = k_w != nullptr && i < k_norm_cols;
-        const float v = rotated(k + (size_t)g * kd, normed ? k_w + (size_t)g * kd : nullptr, normed ? inv_k : 1.0f, d, k_rot_off, rot, pos);
+        const float v = rotated(k + (size_t)g * kd, normed ? k_w + (size_t)g * kd : nullptr, normed ? inv_k : 1.0f, d, k_rot_off, rot, cs);
         T* dst = k_pages + (((size_t)page * G + g) * page_size + in_page) * kd;
         pb_st(dst + pb_kv_elem_offset(d, in_page, swizzle_k), v);
     }
@@ -146,6 +152,7 @@ PB_API int pb_qkv_prepare(const void* q_in, long long ldq, const void* k_in, lon
         PB_REQUIRE(!swizzle_k || kd % 8 == 0, "qkv_prepare: permuted key rows need a size in multiples of 8");
         PB_REQUIRE(!swizzle_v || vd % 8 == 0, "qkv_prepare: permuted value rows need a size in multiples of 8");
     }
+    PB_REQUIRE(rot_dims <= 8192, "qkv_prepare: a rotation of %d elements", rot_dims);
     if (n_tokens == 0) return 0;
     int work = H * qd;
     if (k_pages != nullptr && G * kd > work) work = G * kd;
@@ -153,7 +160,7 @@ PB_API int pb_qkv_prepare(const void* q_in, long long ldq, const void* k_in, lon
     while (threads < 512 && threads < work) threads <<= 1;
     RotArgs rot{rates, rot_dims, adjacent, amplitude};
     PB_DISPATCH_DTYPE(dtype, T,
-        (pb_launch(qkv_prepare_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, (const T*)q_in, ldq, (const T*)k_in, ldk,
+        (pb_launch(qkv_prepare_kernel<T>, dim3(n_tokens), dim3(threads), rates ? (size_t)rot_dims * sizeof(float) : 0, stream, (const T*)q_in, ldq, (const T*)k_in, ldk,
                    (const T*)v_in, ldv, q_w, k_w, k_norm_cols, eps, rot, q_rot_off, k_rot_off, positions, table_row, block_table,
                    table_stride, page_size, num_pages, (T*)q_out, q_split, (T*)q_out2, q2_head_stride, q2_off, (T*)k_pages,
                    (T*)v_pages, H, qd, G, kd, Gv, vd, swizzle_k, swizzle_v, status)));

@@ -21,6 +21,26 @@
 namespace {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ bool pb_aligned_dev(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+// 16 bytes of a row as floats: 4 of float32, 8 of bfloat16
+__device__ __forceinline__ void pb_ld_vec(const float* p, float (&out)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+__device__ __forceinline__ void pb_ld_vec(const __nv_bfloat16* p, float (&out)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void pb_st_vec(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void pb_st_vec(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -49,6 +69,62 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, long long ld_i
     pb_st(out + (size_t)t * channels + c, silu_f(acc));
 }
 
+// The same, 16 bytes of channels per thread and a run of consecutive tokens per block (channels, row stride and
+// pointers in multiples of 16 bytes; TAPS known at compile time).  A thread keeps its channels' taps and the last
+// TAPS - 1 inputs in registers: while the run stays inside one sequence every input is read once.
+#define CONV_RUN 16
+template <typename T, int TAPS>
+__global__ void causal_conv_silu_vec_kernel(const T* __restrict__ in, long long ld_in, const float* __restrict__ w,
+                                            const float* __restrict__ bias, const T* __restrict__ carried, T* __restrict__ out,
+                                            const int32_t* __restrict__ token_seq, const int32_t* __restrict__ positions,
+                                            const int32_t* __restrict__ q_start, const int32_t* __restrict__ slots, int n_tokens,
+                                            int channels) {
+    constexpr int VN = 16 / sizeof(T);
+    pb_grid_dep_launch();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VN;
+    if (c >= channels) return;
+    float wt[VN][TAPS], bs[VN];
+#pragma unroll
+    for (int e = 0; e < VN; ++e) {
+        bs[e] = bias[c + e];
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wt[e][j] = w[(size_t)(c + e) * TAPS + j];
+    }
+    pb_grid_dep_wait();
+    float win[TAPS][VN];                                   // win[j]: the input under tap j
+    int prev_seq = -1;
+    const int t_end = min(n_tokens, (int)(blockIdx.x + 1) * CONV_RUN);
+    for (int t = blockIdx.x * CONV_RUN; t < t_end; ++t) {
+        const int seq = token_seq[t];
+        if (seq < 0) { prev_seq = -1; continue; }          // a padding row
+        const int i = positions[t] - q_start[seq];
+        if (seq == prev_seq) {                             // the token after the one before: shift, fetch one
+#pragma unroll
+            for (int j = 0; j + 1 < TAPS; ++j)
+#pragma unroll
+                for (int e = 0; e < VN; ++e) win[j][e] = win[j + 1][e];
+            pb_ld_vec(in + (size_t)t * ld_in + c, win[TAPS - 1]);
+        } else {
+            const T* old = carried + (size_t)slots[seq] * (TAPS - 1) * channels;
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) {
+                const int idx = i - (TAPS - 1 - j);
+                pb_ld_vec(idx >= 0 ? in + (size_t)(t - (TAPS - 1 - j)) * ld_in + c : old + (size_t)(TAPS - 1 + idx) * channels + c, win[j]);
+            }
+            prev_seq = seq;
+        }
+        float acc[VN];
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+            float a = bs[e];
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) a = fmaf(wt[e][j], win[j][e], a);
+            acc[e] = silu_f(a);
+        }
+        pb_st_vec(out + (size_t)t * channels + c, acc);
+    }
+}
+
 // Row s of a sequence's carried inputs holds the input at in-step index s - (taps - 1) of its NEXT step.  One thread
 // owns a (sequence, channel): it reads rows above the one it writes, in ascending order, so nothing is lost.
 template <typename T>
@@ -69,82 +145,158 @@ __global__ void conv_state_update_kernel(const T* __restrict__ in, long long ld_
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// The scan.  A block is 128 threads = 16 columns p of a head's state x 8 lanes over the state rows n; lane j of a
-// column keeps rows n = j, j + 8, ... in registers (NPL of them).  Per token: one decay and step size per head,
-// S[n][p] = decay S[n][p] + (dt x[p]) B[n], y[p] = sum_n S[n][p] C[n] (own rows in ascending order, then the
-// 8 lanes by three exchanges) + D x[p].  The next token's inputs are fetched while this one's are used.
+// The scan.  A block is eight warps on one head's state, 16 columns p of it.  Warps 0-3 compute: 16 columns x 8 lanes
+// over the state rows n, a lane keeping NPL rows in registers (rows 4 (8 i + j) .. + 3 for i = 0 .. NPL / 4 - 1, so
+// that the lanes of a column read consecutive 16-byte pieces of B and C).  Warps 4-7 load: while the others work on
+// one chunk of tokens they put the next chunk's x, B, C (as float32), step size dt = softplus(dt + bias) and decay
+// exp(-exp(A_log) dt) into the other half of shared memory, so the recurrence, which visits tokens one after the
+// other, never waits for global memory.  Per token: S[n][p] = decay S[n][p] + (dt x[p]) B[n],
+// y[p] = sum_n S[n][p] C[n] (own rows in ascending order, then the 8 lanes by three exchanges) + D x[p].
 #define SCAN_COLS 16
 #define SCAN_LANES 8
 
 template <typename T, int NPL>
-__global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES)
+__global__ void __launch_bounds__(256)
 ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long ld_dt, const float* __restrict__ dt_bias,
                 const float* __restrict__ a_log, const float* __restrict__ d_skip, float* __restrict__ state,
                 float* __restrict__ y, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ slots, int heads, int P,
                 int N, int groups) {
+    constexpr int NPAD = NPL * SCAN_LANES;                     // state rows with padding: a power of two
+    constexpr int CHUNK = NPL == 32 ? 8 : 16;                  // tokens per chunk
+    constexpr int BUF = CHUNK * (2 * NPAD + SCAN_COLS + 2);    // floats per half: B, C, x, dt, decay
+    __shared__ __align__(16) float sm[2 * BUF];
     pb_grid_dep_launch();
     const int col_blocks = (P + SCAN_COLS - 1) / SCAN_COLS;
-    const int h = blockIdx.x / col_blocks;
-    const int p = (blockIdx.x % col_blocks) * SCAN_COLS + threadIdx.x / SCAN_LANES;
-    const int j = threadIdx.x % SCAN_LANES;
+    const int h = blockIdx.x / col_blocks, p_first = (blockIdx.x % col_blocks) * SCAN_COLS;
     const int r = blockIdx.y;
+    const int tid = threadIdx.x;
+    const bool computes = tid < SCAN_COLS * SCAN_LANES;
     const float neg_a = -expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];     // written by no kernel: before the wait
     pb_grid_dep_wait();
     const int first = cu_q[r], n_tok = cu_q[r + 1] - first;
     if (n_tok <= 0) return;
-    const bool live = p < P;
     const int inner = heads * P, channels = inner + 2 * groups * N;
     const int g = h / (heads / groups);
-    const int pp = live ? p : P - 1;                                              // idle columns follow along and store nothing
+    const int n_chunks = (n_tok + CHUNK - 1) / CHUNK;
+
+    // compute threads
+    const int colp = tid / SCAN_LANES, j = tid % SCAN_LANES;
+    const int p = p_first + colp;
+    const bool live = computes && p < P;
+    const int pp = p < P ? p : P - 1;                                             // idle columns follow along and store nothing
     float* S = state + (((size_t)slots[r] * heads + h) * N) * P + pp;
     float s[NPL];
+    if (computes) {
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) { const int n = j + SCAN_LANES * i; s[i] = n < N ? S[(size_t)n * P] : 0.f; }
-
-    const T* row = u + (size_t)first * channels;
-    float x = pb_ld(row + h * P + pp), dt_raw = pb_ld(dt_in + (size_t)first * ld_dt + h);
-    float b[NPL], c[NPL];
-#pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-        const int n = j + SCAN_LANES * i;
-        b[i] = n < N ? pb_ld(row + inner + g * N + n) : 0.f;
-        c[i] = n < N ? pb_ld(row + inner + groups * N + g * N + n) : 0.f;
+        for (int i = 0; i < NPL; ++i) { const int n = ((i >> 2) * SCAN_LANES + j) * 4 + (i & 3); s[i] = n < N ? S[(size_t)n * P] : 0.f; }
     }
-    for (int t = 0; t < n_tok; ++t) {
-        float x_next = 0.f, dt_next = 0.f, b_next[NPL], c_next[NPL];
-        const bool more = t + 1 < n_tok;
-        const T* nrow = row + channels;
-        if (more) {
-            x_next = pb_ld(nrow + h * P + pp);
-            dt_next = pb_ld(dt_in + (size_t)(first + t + 1) * ld_dt + h);
-        }
+    // load threads
+    const int lt = tid - SCAN_COLS * SCAN_LANES;
+    constexpr int VN = 16 / sizeof(T);                                            // elements of a 16-byte load
+    const bool vec = N % VN == 0 && channels % VN == 0 && inner % VN == 0 && pb_aligned_dev(u, 16);
+    if (N < NPAD) {                                                               // rows past N are read as zeros by the lanes
+        if (!computes)
+            for (int idx = lt; idx < 2 * BUF; idx += 128) sm[idx] = 0.f;
+        __syncthreads();
+    }
+    auto load_chunk = [&](int k) {
+        float* buf = sm + (k & 1) * BUF;
+        const int t0 = k * CHUNK, cnt = min(CHUNK, n_tok - t0);
+        const T* rows = u + (size_t)(first + t0) * channels;
+        if (vec) {
+            // B and C of a token: 2 N / VN pieces of 16 bytes; four of a thread's loads in flight at a time
+            const int per_tok = 2 * (N / VN), total = cnt * per_tok;
+            for (int base = lt; base < total; base += 4 * 128) {
+                float v[4][VN];
 #pragma unroll
-        for (int i = 0; i < NPL; ++i) {
-            const int n = j + SCAN_LANES * i;
-            b_next[i] = (more && n < N) ? pb_ld(nrow + inner + g * N + n) : 0.f;
-            c_next[i] = (more && n < N) ? pb_ld(nrow + inner + groups * N + g * N + n) : 0.f;
-        }
-        const float dt = softplus_f(dt_raw + bias);
-        const float decay = expf(neg_a * dt), dx = dt * x;
-        float acc = 0.f;
+                for (int it = 0; it < 4; ++it) {
+                    const int idx = base + it * 128;
+                    if (idx < total) {
+                        const int tt = idx / per_tok, rem = idx - tt * per_tok;
+                        pb_ld_vec(rows + (size_t)tt * channels + inner + g * N + (rem >= N / VN ? (groups - 1) * N : 0) + rem * VN, v[it]);
+                    }
+                }
 #pragma unroll
-        for (int i = 0; i < NPL; ++i) {
-            s[i] = fmaf(decay, s[i], dx * b[i]);
-            acc = fmaf(s[i], c[i], acc);
-        }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-        if (live && j == 0) y[(size_t)(first + t) * inner + h * P + p] = fmaf(skip, x, acc);
-        x = x_next;
-        dt_raw = dt_next;
+                for (int it = 0; it < 4; ++it) {
+                    const int idx = base + it * 128;
+                    if (idx < total) {
+                        const int tt = idx / per_tok, rem = idx - tt * per_tok;
+                        const bool is_c = rem >= N / VN;
+                        float* dst = buf + (is_c ? CHUNK * NPAD : 0) + tt * NPAD + (is_c ? rem - N / VN : rem) * VN;
 #pragma unroll
-        for (int i = 0; i < NPL; ++i) { b[i] = b_next[i]; c[i] = c_next[i]; }
-        row = nrow;
+                        for (int e = 0; e < VN; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(v[it][e], v[it][e + 1], v[it][e + 2], v[it][e + 3]);
+                    }
+                }
+            }
+        } else {
+            for (int base = lt; base < cnt * N; base += 4 * 128) {
+                float vb[4], vc[4];
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int idx = base + it * 128;
+                    if (idx < cnt * N) {
+                        const int tt = idx / N, n = idx - tt * N;
+                        const T* row = rows + (size_t)tt * channels + inner + g * N;
+                        vb[it] = pb_ld(row + n);
+                        vc[it] = pb_ld(row + groups * N + n);
+                    }
+                }
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int idx = base + it * 128;
+                    if (idx < cnt * N) {
+                        const int tt = idx / N, n = idx - tt * N;
+                        buf[tt * NPAD + n] = vb[it];
+                        buf[CHUNK * NPAD + tt * NPAD + n] = vc[it];
+                    }
+                }
+            }
+        }
+        for (int idx = lt; idx < cnt * SCAN_COLS; idx += 128) {
+            const int tt = idx / SCAN_COLS, cc = idx % SCAN_COLS;
+            buf[2 * CHUNK * NPAD + idx] = p_first + cc < P ? pb_ld(rows + (size_t)tt * channels + h * P + p_first + cc) : 0.f;
+        }
+        if (lt < cnt) {
+            const float dt = softplus_f(pb_ld(dt_in + (size_t)(first + t0 + lt) * ld_dt + h) + bias);
+            buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + lt] = dt;
+            buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + CHUNK + lt] = expf(neg_a * dt);
+        }
+    };
+    if (!computes) load_chunk(0);
+    __syncthreads();
+    for (int k = 0; k < n_chunks; ++k) {
+        if (!computes) {
+            if (k + 1 < n_chunks) load_chunk(k + 1);
+        } else {
+            const float* buf = sm + (k & 1) * BUF;
+            const int t0 = k * CHUNK, cnt = min(CHUNK, n_tok - t0);
+            for (int tt = 0; tt < cnt; ++tt) {
+                const float x = buf[2 * CHUNK * NPAD + tt * SCAN_COLS + colp];
+                const float dt = buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + tt], decay = buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + CHUNK + tt];
+                const float dx = dt * x;
+                const float4* b4 = reinterpret_cast<const float4*>(buf + tt * NPAD) + j;
+                const float4* c4 = reinterpret_cast<const float4*>(buf + CHUNK * NPAD + tt * NPAD) + j;
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;                   // four sums side by side, added up in a fixed order
+#pragma unroll
+                for (int i = 0; i < NPL / 4; ++i) {
+                    const float4 b = b4[i * SCAN_LANES], c = c4[i * SCAN_LANES];
+                    s[4 * i + 0] = fmaf(decay, s[4 * i + 0], dx * b.x); a0 = fmaf(s[4 * i + 0], c.x, a0);
+                    s[4 * i + 1] = fmaf(decay, s[4 * i + 1], dx * b.y); a1 = fmaf(s[4 * i + 1], c.y, a1);
+                    s[4 * i + 2] = fmaf(decay, s[4 * i + 2], dx * b.z); a2 = fmaf(s[4 * i + 2], c.z, a2);
+                    s[4 * i + 3] = fmaf(decay, s[4 * i + 3], dx * b.w); a3 = fmaf(s[4 * i + 3], c.w, a3);
+                }
+                float acc = (a0 + a1) + (a2 + a3);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+                if (live && j == 0) y[(size_t)(first + t0 + tt) * inner + h * P + p] = fmaf(skip, x, acc);
+            }
+        }
+        __syncthreads();
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < NPL; ++i) { const int n = j + SCAN_LANES * i; if (n < N) S[(size_t)n * P] = s[i]; }
+        for (int i = 0; i < NPL; ++i) { const int n = ((i >> 2) * SCAN_LANES + j) * 4 + (i & 3); if (n < N) S[(size_t)n * P] = s[i]; }
     }
 }
 
@@ -191,6 +343,19 @@ PB_API int pb_causal_conv_silu(const void* in, long long ld_in, const float* w, 
     PB_REQUIRE(in && w && bias && out && token_seq && positions && q_start && slots && (taps == 1 || carried), "causal_conv_silu: null pointer");
     if (n_tokens == 0) return 0;
     PB_REQUIRE((channels + 127) / 128 < 65536, "causal_conv_silu: %d channels in one launch", channels);
+    const int vn = dtype == PB_BF16 ? 8 : 4;
+    if (taps >= 2 && taps <= 4 && channels % vn == 0 && ld_in % vn == 0 && pb_aligned(in, 16) && pb_aligned(out, 16) && pb_aligned(carried, 16)) {
+        const dim3 grid((n_tokens + CONV_RUN - 1) / CONV_RUN, (channels / vn + 63) / 64);
+#define CONV_LAUNCH(TAPS)                                                                                                     \
+    PB_DISPATCH_DTYPE(dtype, T, (pb_launch(causal_conv_silu_vec_kernel<T, TAPS>, grid, dim3(64), 0, stream, (const T*)in, ld_in, w, bias, \
+                                           (const T*)carried, (T*)out, token_seq, positions, q_start, slots, n_tokens, channels)))
+        if (taps == 2) CONV_LAUNCH(2);
+        else if (taps == 3) CONV_LAUNCH(3);
+        else CONV_LAUNCH(4);
+#undef CONV_LAUNCH
+        PB_CHECK_LAUNCH("causal_conv_silu");
+        return 0;
+    }
     PB_DISPATCH_DTYPE(dtype, T,
         (pb_launch(causal_conv_silu_kernel<T>, dim3(n_tokens, (channels + 127) / 128), dim3(128), 0, stream, (const T*)in, ld_in, w, bias,
                    (const T*)carried, (T*)out, token_seq, positions, q_start, slots, n_tokens, channels, taps)));
@@ -223,7 +388,7 @@ PB_API int pb_ssm_scan(const void* u, const void* dt_in, long long ld_dt, int dt
     if (n_seqs == 0) return 0;
     PB_REQUIRE(n_seqs < 65536, "ssm_scan: %d sequences in one launch", n_seqs);
     const int col_blocks = (P + SCAN_COLS - 1) / SCAN_COLS;
-    const dim3 grid(heads * col_blocks, n_seqs), block(SCAN_COLS * SCAN_LANES);
+    const dim3 grid(heads * col_blocks, n_seqs), block(2 * SCAN_COLS * SCAN_LANES);
     const int npl = (N + SCAN_LANES - 1) / SCAN_LANES;
 #define SCAN_LAUNCH(NPL)                                                                                                    \
     PB_DISPATCH_DTYPE(dtype, T, (pb_launch(ssm_scan_kernel<T, NPL>, grid, block, 0, stream, (const T*)u, (const T*)dt_in, ld_dt, \

@@ -64,7 +64,9 @@ def attention_general(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[
     blocks = n_tiles * G * (-(-(H // G) // 32))
     splits = 1
     if blocks < _sm_count(q.device):
-        splits = max(1, min(MAX_SPLITS, -(-2 * _sm_count(q.device) // blocks), -(-max_ctx // 32)))
+        key_tiles = -(-max_ctx // 32)
+        splits = max(1, min(MAX_SPLITS, -(-2 * _sm_count(q.device) // blocks), key_tiles))
+        splits = -(-key_tiles // -(-key_tiles // splits))               # as many blocks as have tiles to work on
     scratch = None
     if splits > 1:
         scratch = batch.workspace("general_attention_parts", (lib.pb_attention_paged_tc_scratch_floats(T, H, value_dim, splits),), torch.float32)
