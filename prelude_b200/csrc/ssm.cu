@@ -203,6 +203,15 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
         float* buf = sm + (k & 1) * BUF;
         const int t0 = k * CHUNK, cnt = min(CHUNK, n_tok - t0);
         const T* rows = u + (size_t)(first + t0) * channels;
+        // everything a thread fetches for the chunk is asked for before anything is stored: one wait per chunk
+        float xv[(CHUNK * SCAN_COLS + 127) / 128];
+#pragma unroll
+        for (int it = 0; it < (CHUNK * SCAN_COLS + 127) / 128; ++it) {
+            const int idx = lt + it * 128;
+            const int tt = idx / SCAN_COLS, cc = idx % SCAN_COLS;
+            xv[it] = (idx < cnt * SCAN_COLS && p_first + cc < P) ? pb_ld(rows + (size_t)tt * channels + h * P + p_first + cc) : 0.f;
+        }
+        const float dt_raw = lt < cnt ? pb_ld(dt_in + (size_t)(first + t0 + lt) * ld_dt + h) : 0.f;
         if (vec) {
             // B and C of a token: 2 N / VN pieces of 16 bytes; four of a thread's loads in flight at a time
             const int per_tok = 2 * (N / VN), total = cnt * per_tok;
@@ -252,12 +261,13 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
                 }
             }
         }
-        for (int idx = lt; idx < cnt * SCAN_COLS; idx += 128) {
-            const int tt = idx / SCAN_COLS, cc = idx % SCAN_COLS;
-            buf[2 * CHUNK * NPAD + idx] = p_first + cc < P ? pb_ld(rows + (size_t)tt * channels + h * P + p_first + cc) : 0.f;
+#pragma unroll
+        for (int it = 0; it < (CHUNK * SCAN_COLS + 127) / 128; ++it) {
+            const int idx = lt + it * 128;
+            if (idx < cnt * SCAN_COLS) buf[2 * CHUNK * NPAD + idx] = xv[it];
         }
         if (lt < cnt) {
-            const float dt = softplus_f(pb_ld(dt_in + (size_t)(first + t0 + lt) * ld_dt + h) + bias);
+            const float dt = softplus_f(dt_raw + bias);
             buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + lt] = dt;
             buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + CHUNK + lt] = expf(neg_a * dt);
         }
