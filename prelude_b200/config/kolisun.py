@@ -78,9 +78,7 @@ def _state_space(m: _Reader, width: int, eps: float, problems: list) -> StateSpa
 
 def _latent_attention(m: _Reader, width: int, eps: float, problems: list) -> LatentAttentionSpec:
     rot_dim = m.positive_int("rot_dim")
-    position = _rotary(m, False, rot_dim, problems)
-    if position.dims != rot_dim:
-        problems.append(f"{m.where}: rot.dims={position.dims} must equal rot_dim={rot_dim}")
+    position = _rotary(m, False, rot_dim, problems)     # turns the first rot.dims elements of the rotated part
     return LatentAttentionSpec(hidden_size=width, num_heads=m.positive_int("heads"), head_dim=m.positive_int("dim"), rot_dim=rot_dim,
                                value_dim=m.positive_int("vdim"), kv_rank=m.positive_int("kv_rank"), q_rank=m.positive_int("q_rank"),
                                softmax_scale=m.number("scale", positive=True), norm_eps=eps, position=position, sink=True)

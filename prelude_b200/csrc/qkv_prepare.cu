@@ -31,6 +31,25 @@ __device__ __forceinline__ float qp_block_sum(float v, float* red) {
     return total;
 }
 
+__device__ __forceinline__ void qp_ld_vec(const float* p, float (&out)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+__device__ __forceinline__ void qp_ld_vec(const __nv_bfloat16* p, float (&out)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void qp_st_vec(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void qp_st_vec(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
 struct RotArgs {
     const float* rates;
     int dims, adjacent;
@@ -123,6 +142,87 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, long long ldq, co
     }
 }
 
+
+// The same with the token's projections staged in shared memory as float32: one pass over global memory with 16-byte
+// loads, sums and rotation partners from shared memory, 16-byte stores.  Takes rows whose q, k and v parts start on
+// 16-byte boundaries and have sizes in multiples of 8 (bfloat16) or 4 (float32) elements, heads and split points likewise.
+template <typename T>
+__global__ void qkv_prepare_staged_kernel(const T* __restrict__ q_in, long long ldq, const T* __restrict__ k_in, long long ldk,
+                                          const T* __restrict__ v_in, long long ldv, const float* __restrict__ q_w,
+                                          const float* __restrict__ k_w, int k_norm_cols, float eps, RotArgs rot, int q_rot_off,
+                                          int k_rot_off, const int32_t* __restrict__ positions, const int32_t* __restrict__ table_row,
+                                          const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
+                                          T* __restrict__ q_out, int q_split, T* __restrict__ q_out2, long long q2_head_stride,
+                                          long long q2_off, T* __restrict__ k_pages, T* __restrict__ v_pages, int H, int qd, int G,
+                                          int kd, int Gv, int vd, int swizzle_k, int swizzle_v, int* __restrict__ status) {
+    constexpr int VN = 16 / sizeof(T);
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    __shared__ float red[32];
+    extern __shared__ float sm[];
+    const int nq = H * qd, nk = k_pages ? G * kd : 0;
+    float* cs = sm;                                       // cosine and sine of the token's angles
+    float* qs = sm + rot.dims;
+    float* ks = qs + nq;
+    const int t = blockIdx.x;
+    const int row = table_row[t];
+    if (row < 0) return;
+    const int p = positions[t];
+    if (rot.rates != nullptr)
+        for (int i = threadIdx.x; i < rot.dims / 2; i += blockDim.x) {
+            float sn, c;
+            sincosf((float)p * rot.rates[i], &sn, &c);
+            cs[2 * i] = c * rot.amplitude;
+            cs[2 * i + 1] = sn * rot.amplitude;
+        }
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = threadIdx.x * VN; i < nq; i += blockDim.x * VN) {
+        float v[VN];
+        qp_ld_vec(q_in + (size_t)t * ldq + i, v);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) { qs[i + e] = v[e]; ssq += v[e] * v[e]; }
+    }
+    for (int i = threadIdx.x * VN; i < nk; i += blockDim.x * VN) {
+        float v[VN];
+        qp_ld_vec(k_in + (size_t)t * ldk + i, v);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) { ks[i + e] = v[e]; if (i + e < k_norm_cols) ssk += v[e] * v[e]; }
+    }
+    const float tq = qp_block_sum(ssq, red), tk = qp_block_sum(ssk, red);          // the barriers also publish the staged rows
+    const float inv_q = q_w ? 1.0f / sqrtf(tq / (float)nq + eps) : 1.0f;
+    const float inv_k = k_w ? 1.0f / sqrtf(tk / (float)k_norm_cols + eps) : 1.0f;
+    for (int i = threadIdx.x * VN; i < nq; i += blockDim.x * VN) {
+        const int h = i / qd, d0 = i - h * qd;
+        float v[VN];
+#pragma unroll
+        for (int e = 0; e < VN; ++e) v[e] = rotated(qs + (size_t)h * qd, q_w ? q_w + (size_t)h * qd : nullptr, inv_q, d0 + e, q_rot_off, rot, cs);
+        if (d0 < q_split) qp_st_vec(q_out + ((size_t)t * H + h) * q_split + d0, v);
+        else qp_st_vec(q_out2 + ((size_t)t * H + h) * q2_head_stride + q2_off + (d0 - q_split), v);
+    }
+    if (k_pages == nullptr) return;
+    const int page = block_table[(size_t)row * table_stride + p / page_size];
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 2);
+        return;
+    }
+    const int in_page = p % page_size;
+    for (int i = threadIdx.x * VN; i < nk; i += blockDim.x * VN) {
+        const int g = i / kd, d0 = i - g * kd;
+        const bool normed = k_w != nullptr && i < k_norm_cols;
+        float v[VN];
+#pragma unroll
+        for (int e = 0; e < VN; ++e) v[e] = rotated(ks + (size_t)g * kd, normed ? k_w + (size_t)g * kd : nullptr, normed ? inv_k : 1.0f, d0 + e, k_rot_off, rot, cs);
+        T* dst = k_pages + (((size_t)page * G + g) * page_size + in_page) * kd;
+        qp_st_vec(dst + pb_kv_elem_offset(d0, in_page, swizzle_k), v);
+    }
+    if (v_pages == nullptr || v_in == nullptr) return;
+    for (int i = threadIdx.x * VN; i < Gv * vd; i += blockDim.x * VN) {
+        const int g = i / vd, d0 = i - g * vd;
+        T* dst = v_pages + (((size_t)page * Gv + g) * page_size + in_page) * vd;
+        *reinterpret_cast<uint4*>(dst + pb_kv_elem_offset(d0, in_page, swizzle_v)) = *reinterpret_cast<const uint4*>(v_in + (size_t)t * ldv + i);
+    }
+}
+
 }  // namespace
 
 PB_API int pb_qkv_prepare(const void* q_in, long long ldq, const void* k_in, long long ldk, const void* v_in, long long ldv,
@@ -158,7 +258,25 @@ PB_API int pb_qkv_prepare(const void* q_in, long long ldq, const void* k_in, lon
     if (k_pages != nullptr && G * kd > work) work = G * kd;
     int threads = 64;
     while (threads < 512 && threads < work) threads <<= 1;
-    RotArgs rot{rates, rot_dims, adjacent, amplitude};
+    RotArgs rot{rates, rates ? rot_dims : 0, adjacent, amplitude};
+    const int vn = dtype == PB_BF16 ? 8 : 4;
+    const size_t esz = dtype == PB_BF16 ? 2 : 4;
+    const size_t staged_bytes = ((size_t)rot.dims + (size_t)H * qd + (k_pages ? (size_t)G * kd : 0)) * sizeof(float);
+    bool staged = staged_bytes <= 40 * 1024 && qd % vn == 0 && q_split % vn == 0 && ldq % vn == 0 && pb_aligned(q_in, 16) && pb_aligned(q_out, 16) &&
+                  (q_split == qd || (q2_head_stride % vn == 0 && q2_off % vn == 0 && pb_aligned(q_out2, 16)));
+    if (staged && k_pages != nullptr)
+        staged = kd % vn == 0 && ldk % vn == 0 && pb_aligned(k_in, 16) && pb_aligned(k_pages, 16) && k_norm_cols % vn == 0 &&
+                 (v_pages == nullptr || (vd % vn == 0 && ldv % vn == 0 && pb_aligned(v_in, 16) && pb_aligned(v_pages, 16)));
+    if (staged) {
+        PB_DISPATCH_DTYPE(dtype, T,
+            (pb_launch(qkv_prepare_staged_kernel<T>, dim3(n_tokens), dim3(threads >= 128 ? threads / 2 : threads), staged_bytes, stream, (const T*)q_in, ldq,
+                       (const T*)k_in, ldk, (const T*)v_in, ldv, q_w, k_w, k_norm_cols, eps, rot, q_rot_off, k_rot_off, positions, table_row,
+                       block_table, table_stride, page_size, num_pages, (T*)q_out, q_split, (T*)q_out2, q2_head_stride, q2_off, (T*)k_pages,
+                       (T*)v_pages, H, qd, G, kd, Gv, vd, swizzle_k, swizzle_v, status)));
+        PB_CHECK_LAUNCH("qkv_prepare");
+        return 0;
+    }
+    (void)esz;
     PB_DISPATCH_DTYPE(dtype, T,
         (pb_launch(qkv_prepare_kernel<T>, dim3(n_tokens), dim3(threads), rates ? (size_t)rot_dims * sizeof(float) : 0, stream, (const T*)q_in, ldq, (const T*)k_in, ldk,
                    (const T*)v_in, ldv, q_w, k_w, k_norm_cols, eps, rot, q_rot_off, k_rot_off, positions, table_row, block_table,

@@ -153,9 +153,9 @@ def test_window_attention_mixer_equals_the_plain_one(dtype, heads, kv, dim, vdim
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("heads,dim,rot,vdim,kv_rank,q_rank,page", [(3, 12, 6, 20, 10, 14, 4), (4, 32, 16, 48, 64, 40, 16), (1, 16, 16, 16, 16, 16, 8),
-                                                                    (8, 16, 32, 16, 32, 64, 16), (2, 7, 4, 9, 13, 5, 8)])
-def test_latent_attention_mixer_equals_the_plain_one(dtype, heads, dim, rot, vdim, kv_rank, q_rank, page):
+@pytest.mark.parametrize("heads,dim,rot,vdim,kv_rank,q_rank,page,turned", [(3, 12, 6, 20, 10, 14, 4, 6), (4, 32, 16, 48, 64, 40, 16, 16), (1, 16, 16, 16, 16, 16, 8, 16),
+                                                                           (8, 16, 32, 16, 32, 64, 16, 32), (2, 7, 4, 9, 13, 5, 8, 4), (4, 32, 16, 32, 64, 24, 16, 8)])
+def test_latent_attention_mixer_equals_the_plain_one(dtype, heads, dim, rot, vdim, kv_rank, q_rank, page, turned):
     """The latent attention alone over a prompt and token by token, with sinks large enough to take a good share of
     every softmax (one left out shows at once) and an early token that later queries find among a hundred."""
     from prelude_b200.config.spec import LatentAttentionSpec, RotaryRampScaling, RotaryRatesSpec
@@ -163,7 +163,7 @@ def test_latent_attention_mixer_equals_the_plain_one(dtype, heads, dim, rot, vdi
     width, T, head_tokens = 40, 120, 83
     g = torch.Generator().manual_seed(heads * 100 + kv_rank)
     m = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": 2.0 / math.sqrt(dim + rot),
-         "rot": {"dims": rot, "base": 300.0, "scaling": kt.ramp(3.0, 24, 6.0, 1.0)}}
+         "rot": {"dims": turned, "base": 300.0, "scaling": kt.ramp(3.0, 24, 6.0, 1.0)}}
     w = {"dq": torch.randn(q_rank, width, generator=g) * 0.3, "dq.norm": 1.0 + 0.3 * torch.randn(q_rank, generator=g),
          "uq": torch.randn(heads * (dim + rot), q_rank, generator=g) * 0.4, "dkv": torch.randn(kv_rank + rot, width, generator=g) * 0.3,
          "dkv.norm": 1.0 + 0.3 * torch.randn(kv_rank, generator=g), "uk": torch.randn(heads * dim, kv_rank, generator=g) * 0.4,
@@ -177,7 +177,7 @@ def test_latent_attention_mixer_equals_the_plain_one(dtype, heads, dim, rot, vdi
     no_sink = plain.latent_attention(x.double(), {k: (v.double() if k != "sink" else v.double() - 50.0) for k, v in w.items()}, m, 1e-5)
     assert float((want - no_sink).abs().max()) > 0.02 * float(want.abs().max())          # the sinks matter here
     spec = LatentAttentionSpec(width, heads, dim, rot, vdim, kv_rank, q_rank, m["scale"], 1e-5,
-                               RotaryRatesSpec(rot, 300.0, False, RotaryRampScaling(3.0, 24, 6.0, 1.0)), sink=True)
+                               RotaryRatesSpec(turned, 300.0, False, RotaryRampScaling(3.0, 24, 6.0, 1.0)), sink=True)
     part = make_part("mixer", spec, "mix")
     part.load(lambda name: w[name[len("mix."):]], RunContext(torch.device(DEV), dtype))
     tol = 5e-5 if dtype == torch.float32 else 4e-2

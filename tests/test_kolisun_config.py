@@ -56,7 +56,7 @@ def test_tensor_list_has_the_designs_names_and_shapes():
     (lambda c: c["layers"][1]["mixer"]["left"].update(heads=5), "not a multiple"),
     (lambda c: c["layers"][1]["mixer"]["right"].update(groups=3), "not a multiple"),
     (lambda c: c["layers"][1]["mixer"]["right"].update(norm_groups=5), "equal parts"),
-    (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=4), "must equal rot_dim"),
+    (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=8), "at most the 6 elements"),
     (lambda c: c["layers"][1]["mixer"]["left"]["rot"].update(dims=7), "even"),
     (lambda c: c["layers"][1]["mixer"].pop("right_scale"), "right_scale"),
     (lambda c: c["layers"][0]["mlp"].update(kind="moe"), "unknown kind"),
