@@ -26,7 +26,7 @@ import copy
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
-from .pabelix import _Reader
+from .reader import _Reader
 from .registry import ConfigError, extract_eos_token_ids, register_architecture
 from .spec import (BlockSpec, GatedMlpSpec, GqaSpec, LatentAttentionSpec, LayerCall, LinearHeadSpec, ModelSpec, NormSpec,
                    ParallelMixerSpec, RotaryBandScaling, RotaryRampScaling, RotaryRatesSpec, StateSpaceSpec)
