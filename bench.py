@@ -24,6 +24,9 @@ Every decode step reads the whole model (8 GB at full size), far more than the
 mixed continuous batch through Engine.generate() (BASELINE.json configs[3]: 32
 requests, prompts of 128 to 2,048 tokens cut into portions of 512 beside the
 running decodes, 256 tokens each), as generated tokens a second by the wall clock.
+``--workload pabelix`` and ``--workload kolisun`` put that design beside Qwen3 dense at equal
+layer sizes (random weights): prefill and decode steps, and the design's kernels beside their
+like, each a line of its own.  None of them changes the default run or its line.
 """
 import argparse
 import json

@@ -260,7 +260,6 @@ PB_API int pb_qkv_prepare(const void* q_in, long long ldq, const void* k_in, lon
     while (threads < 512 && threads < work) threads <<= 1;
     RotArgs rot{rates, rates ? rot_dims : 0, adjacent, amplitude};
     const int vn = dtype == PB_BF16 ? 8 : 4;
-    const size_t esz = dtype == PB_BF16 ? 2 : 4;
     const size_t staged_bytes = ((size_t)rot.dims + (size_t)H * qd + (k_pages ? (size_t)G * kd : 0)) * sizeof(float);
     bool staged = staged_bytes <= 40 * 1024 && qd % vn == 0 && q_split % vn == 0 && ldq % vn == 0 && pb_aligned(q_in, 16) && pb_aligned(q_out, 16) &&
                   (q_split == qd || (q2_head_stride % vn == 0 && q2_off % vn == 0 && pb_aligned(q_out2, 16)));
@@ -276,7 +275,6 @@ PB_API int pb_qkv_prepare(const void* q_in, long long ldq, const void* k_in, lon
         PB_CHECK_LAUNCH("qkv_prepare");
         return 0;
     }
-    (void)esz;
     PB_DISPATCH_DTYPE(dtype, T,
         (pb_launch(qkv_prepare_kernel<T>, dim3(n_tokens), dim3(threads), rates ? (size_t)rot_dims * sizeof(float) : 0, stream, (const T*)q_in, ldq, (const T*)k_in, ldk,
                    (const T*)v_in, ldv, q_w, k_w, k_norm_cols, eps, rot, q_rot_off, k_rot_off, positions, table_row, block_table,
